@@ -1,0 +1,153 @@
+/* h3_gpu.h -- C ABI of the B200 attention library: context, tensors, command
+ * chain and the h3_* attention ops.
+ *
+ * The declarations keep the names, argument order and return conventions of
+ * the reference's h3_gpu.h so that a caller of the reference (qwen_dit.m,
+ * the tests under tests/) links against this library unchanged for the ops on
+ * the attention path.  Each declaration cites the reference interface it
+ * replaces (path:line inside the reference project).
+ *
+ * Conventions (reference h3_gpu.m:267-289, 975-1053):
+ *   - every op returns 1 on success and 0 on failure; the reason is available
+ *     from h3_gpu_error(); creators return NULL on failure;
+ *   - ops only enqueue work; an op called without an open chain fails with
+ *     "h3_gpu_begin() was not called"; errors raised on the device surface at
+ *     h3_gpu_submit();
+ *   - a tensor may be larger than an op needs ("absent or too small" is the
+ *     only size failure), the caller owns every handle, a context is used from
+ *     one thread.
+ */
+#ifndef H3_GPU_H
+#define H3_GPU_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference h3_gpu.h:7-8 */
+typedef struct h3_gpu h3_gpu;
+typedef struct h3_gpu_tensor h3_gpu_tensor;
+
+/* reference h3_gpu.h:14-19 */
+typedef enum {
+    H3_GPU_F32 = 0,
+    H3_GPU_BF16,
+    H3_GPU_I8,
+    H3_GPU_U32
+} h3_gpu_dtype;
+
+/* reference h3_gpu.h:21-37.  Filled here: allocated/live/peak bytes, tensor
+ * allocations, direct_dispatches (kernel launches), blit_copies,
+ * submissions, command_wait_seconds, gpu_seconds (CUDA events around each
+ * chain).  The mps_* counters stay 0. */
+typedef struct {
+    uint64_t allocated_bytes;
+    uint64_t live_bytes;
+    uint64_t peak_live_bytes;
+    uint64_t tensor_allocations;
+    uint64_t direct_dispatches;
+    uint64_t mps_linear_dispatches;
+    uint64_t mps_conv_dispatches;
+    uint64_t mps_sdpa_dispatches;
+    uint64_t blit_copies;
+    uint64_t submissions;
+    double command_encode_seconds;
+    double command_wait_seconds;
+    double gpu_seconds;
+} h3_gpu_stats;
+
+/* reference h3_gpu.h:39-44, h3_gpu.m:380-579.  The shader path is ignored.
+ * The context binds the CUDA device named by QW_CUDA_DEVICE (default: the
+ * calling thread's current device) and owns one stream.  Fails (NULL + message)
+ * when no sm_100 device is present: there is no CPU fallback. */
+h3_gpu *h3_gpu_create(const char *shader_source_path, char *error, size_t error_size);
+void h3_gpu_free(h3_gpu *gpu);
+int h3_gpu_is_m5(const h3_gpu *gpu);        /* always 0 */
+int h3_gpu_has_nax_mlp(const h3_gpu *gpu);  /* always 0 */
+int h3_gpu_has_int8_mlp(const h3_gpu *gpu); /* always 0 */
+/* reference h3_gpu.h:10-12: nothing is cached per shape here; no-op. */
+void h3_gpu_clear_graph_cache(h3_gpu *gpu);
+
+/* reference h3_gpu.h:46-55, h3_gpu.m:621-647 */
+h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_i8(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *gpu, const float *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *gpu, const uint16_t *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *gpu, const uint32_t *values, size_t elements);
+/* reference h3_gpu.h:73-75, h3_gpu.m:887-918; NULL-safe */
+void h3_gpu_tensor_free(h3_gpu_tensor *tensor);
+size_t h3_gpu_tensor_elements(const h3_gpu_tensor *tensor);
+h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *tensor);
+
+/* reference h3_gpu.h:76-91, h3_gpu.m:920-973.  The reference's tensors are
+ * host-visible and these are raw memcpys; here a write is a host-to-device copy
+ * ordered on the context's stream (the host buffer may be reused as soon as
+ * the call returns unless it is pinned memory from qw_gpu_host_alloc, which is
+ * consumed asynchronously), and a read drains the stream first.  Range and
+ * dtype violations return 0. */
+int h3_gpu_tensor_read_f32(const h3_gpu_tensor *tensor, float *values, size_t elements);
+int h3_gpu_tensor_read_f32_range(const h3_gpu_tensor *tensor, size_t source_offset,
+                                 float *values, size_t elements);
+int h3_gpu_tensor_read_bf16(const h3_gpu_tensor *tensor, uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_f32(h3_gpu_tensor *tensor, const float *values, size_t elements);
+int h3_gpu_tensor_write_f32_range(h3_gpu_tensor *tensor, size_t destination_offset,
+                                  const float *values, size_t elements);
+int h3_gpu_tensor_write_bf16(h3_gpu_tensor *tensor, const uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *tensor, size_t destination_offset,
+                                   const uint16_t *values, size_t elements);
+
+/* reference h3_gpu.h:93-97, h3_gpu.m:975-1047.  begin fails when a chain is
+ * already open; continue flushes without waiting; submit waits for the whole
+ * chain and reports any launch error or device-side status. */
+int h3_gpu_begin(h3_gpu *gpu);
+int h3_gpu_continue(h3_gpu *gpu);
+int h3_gpu_submit(h3_gpu *gpu);
+/* reference h3_gpu.h:98, h3_gpu.m:1049-1053; never NULL */
+const char *h3_gpu_error(const h3_gpu *gpu);
+/* reference h3_gpu.h:99, h3_gpu.m:1055-1059 */
+int h3_gpu_get_stats(const h3_gpu *gpu, h3_gpu_stats *stats);
+/* reference h3_gpu.h:102-103; no-ops */
+void h3_gpu_profile_set_label(h3_gpu *gpu, const char *label);
+void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase);
+
+/* reference h3_gpu.h:135-142, h3_gpu.m:1384-1444: element-range copy between
+ * tensors of the same dtype ("invalid BF16 blit range" / "invalid F32 blit
+ * range" on any violation). */
+int h3_gpu_copy_bf16(h3_gpu *gpu, h3_gpu_tensor *destination, size_t destination_offset,
+                     const h3_gpu_tensor *source, size_t source_offset, size_t elements);
+int h3_gpu_copy_f32(h3_gpu *gpu, h3_gpu_tensor *destination, size_t destination_offset,
+                    const h3_gpu_tensor *source, size_t source_offset, size_t elements);
+
+/* reference h3_gpu.h:497-507, h3_gpu.m:1698-1720: full bidirectional
+ * self-attention over [sequence, heads, head_dim]; the second form stores
+ * [heads, sequence, head_dim]. */
+int h3_gpu_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                     const h3_gpu_tensor *key, const h3_gpu_tensor *value, uint32_t sequence,
+                     uint32_t heads, uint32_t head_dim, float scale);
+int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *output,
+                                       const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                       const h3_gpu_tensor *value, uint32_t sequence,
+                                       uint32_t heads, uint32_t head_dim, float scale);
+
+/* reference h3_gpu.h:527-530, h3_gpu.m:4478-4493, h3_shaders.metal:4309-4329:
+ * in-place per-(row, head) RMSNorm, single bf16 rounding of x*inv*w. */
+int h3_gpu_head_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *tensor, const h3_gpu_tensor *weight,
+                              uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                              float epsilon);
+
+/* reference h3_gpu.h:537-543, h3_gpu.m:4642-4693, h3_shaders.metal:4375-4445:
+ * token-causal attention; this variant folds the scale into Q and re-rounds Q
+ * to bf16 before the dot products. */
+int h3_gpu_gqa_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                           const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                           uint32_t sequence, uint32_t query_heads, uint32_t kv_heads,
+                           uint32_t head_dim, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,148 @@
+/* qwen_gpu_ext.h -- the qw_* ops of the DiT attention path, same names,
+ * argument order and conventions as the reference's qwen_gpu_ext.h, plus the
+ * additive entry points this library introduces (marked NEW).  Citations are
+ * path:line inside the reference project.  See h3_gpu.h for the shared
+ * conventions (1 = success, 0 = failure + h3_gpu_error()).
+ *
+ * Layouts: activations are token-major [rows, heads, 128] bf16, contiguous;
+ * RoPE tables are f32 [rows, 64]; norm weights bf16 [128]; kv_limit is a U32
+ * tensor of per-row key counts.  head_dim must be 128 for the attention ops.
+ */
+#ifndef QWEN_GPU_EXT_H
+#define QWEN_GPU_EXT_H
+
+#include "h3_gpu.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference qwen_gpu_ext.h:28-36, h3_gpu.m:5159-5193, h3_shaders.metal:4864-4890:
+ * interleaved complex RoPE on q and k with f32 cos/sin tables of
+ * [row, head_dim/2].  In-place safe. */
+int qw_gpu_qk_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output, h3_gpu_tensor *key_output,
+                        const h3_gpu_tensor *query_input, const h3_gpu_tensor *key_input,
+                        const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                        uint32_t sequence, uint32_t heads, uint32_t head_dim);
+
+/* reference qwen_gpu_ext.h:57-60, h3_gpu.m:5258-5275, h3_shaders.metal:4975-4997:
+ * per-head RMSNorm with the normalised value rounded to bf16 before the
+ * weight multiply (double rounding). */
+int qw_gpu_head_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *tensor, const h3_gpu_tensor *weight,
+                              uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                              float epsilon);
+
+/* reference qwen_gpu_ext.h:116-123, h3_gpu.m:5745-5789: flash SDPA, every query
+ * row sees every key; q_rows may differ from kv_rows. */
+int qw_gpu_flash_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                           const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                           uint32_t q_rows, uint32_t kv_rows, uint32_t heads, uint32_t head_dim,
+                           float scale);
+
+/* reference qwen_gpu_ext.h:125-138, h3_gpu.m:5791-5844, h3_shaders.metal:3061-3272:
+ * prefix-visible SDPA.  kv_limit[q_row] (U32 tensor, >= q_rows elements) caps
+ * the key range of each query row; values are read as int32, negatives count
+ * as 0 and everything is capped at kv_rows.  Grouped-query attention:
+ * heads % kv_heads == 0, q head h reads kv head h * kv_heads / heads. */
+int qw_gpu_flash_sdpa_prefix_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                                  const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                                  const h3_gpu_tensor *kv_limit, uint32_t q_rows,
+                                  uint32_t kv_rows, uint32_t heads, uint32_t kv_heads,
+                                  uint32_t head_dim, float scale);
+
+/* reference qwen_gpu_ext.h:212-219, h3_gpu.m:5903-5953, h3_shaders.metal:5003-5069:
+ * token-causal GQA, scale applied to the fp32 scores. */
+int qw_gpu_gqa_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                           const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                           uint32_t sequence, uint32_t query_heads, uint32_t kv_heads,
+                           uint32_t head_dim, float scale);
+
+/* reference qwen_gpu_ext.h:221-228, h3_gpu.m:5972-6054: full SDPA whose query
+ * length may differ from the key/value length. */
+int qw_gpu_sdpa_rect_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
+                          const h3_gpu_tensor *key, const h3_gpu_tensor *value,
+                          uint32_t query_sequence, uint32_t kv_sequence, uint32_t heads,
+                          uint32_t head_dim, float scale);
+
+/* ---------------------------------------------------------------------- */
+/* NEW entry points (no counterpart in the reference).                     */
+
+/* Fused prologue: per-head RMSNorm of q and k (single rounding, the variant
+ * the DiT block uses: qwen_dit.m:1273-1276) followed by the interleaved RoPE
+ * (qwen_dit.m:1277) in one pass over q and k, in place.  Reproduces the bf16
+ * store the reference has between the two stages.  `batch` items share the
+ * tables: row r of every item uses table row r. */
+int qw_gpu_qk_norm_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
+                             const h3_gpu_tensor *norm_weight_q,
+                             const h3_gpu_tensor *norm_weight_k, const h3_gpu_tensor *rope_cos,
+                             const h3_gpu_tensor *rope_sin, uint32_t batch, uint32_t sequence,
+                             uint32_t heads, uint32_t head_dim, float epsilon);
+
+/* Same, reading query_input/key_input and writing query_output/key_output (the
+ * pairs may alias for in-place use, like qw_gpu_qk_rope_bf16). */
+int qw_gpu_qk_norm_rope_out_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
+                                 h3_gpu_tensor *key_output, const h3_gpu_tensor *query_input,
+                                 const h3_gpu_tensor *key_input,
+                                 const h3_gpu_tensor *norm_weight_q,
+                                 const h3_gpu_tensor *norm_weight_k,
+                                 const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                 uint32_t batch, uint32_t sequence, uint32_t heads,
+                                 uint32_t head_dim, float epsilon);
+
+/* Batched block-causal attention with optional key padding (classifier-free
+ * guidance runs cond/uncond as batch items whose text lengths differ).
+ *   q, out [batch, rows, heads, 128]; k, v [batch, rows, kv_heads, 128]
+ *   kv_limit  U32 tensor with `rows` entries (shared by the batch) or
+ *             batch*rows entries (per item), or NULL for "every key".
+ *   text_len  host array of `batch` entries or NULL; with text_pad != 0 the
+ *             keys text_len[b] <= s < text_pad are invisible for item b and the
+ *             query rows in that window store zeros.
+ * Rows without any visible key store zeros.  batch <= 8. */
+int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                  const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                  const h3_gpu_tensor *value, const h3_gpu_tensor *kv_limit,
+                                  uint32_t batch, uint32_t rows, uint32_t heads,
+                                  uint32_t kv_heads, uint32_t head_dim,
+                                  const uint32_t *text_len, uint32_t text_pad, float scale);
+
+/* Context bound to an explicit CUDA device. */
+h3_gpu *qw_gpu_create_on_device(int device, char *error, size_t error_size);
+int qw_gpu_device(const h3_gpu *gpu);
+/* Interop handles: the tensor's device address and the context's cudaStream_t. */
+void *qw_gpu_tensor_device_ptr(const h3_gpu_tensor *tensor);
+void *qw_gpu_stream(const h3_gpu *gpu);
+/* Pinned host memory for asynchronous tensor writes/reads. */
+void *qw_gpu_host_alloc(size_t bytes);
+void qw_gpu_host_free(void *pointer);
+/* Asynchronous device-to-host read into pinned memory, ordered on the
+ * context's stream; complete after the next h3_gpu_submit(). */
+int qw_gpu_tensor_read_async(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host,
+                             size_t elements);
+/* Select the attention kernel: "sm100" (default) or "scalar" (diagnostic
+ * fp32 kernel).  Returns 0 on an unknown name. */
+int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name);
+/* Launches enqueued by this context's ops since creation (own kernels only). */
+uint64_t qw_gpu_kernel_launches(const h3_gpu *gpu);
+
+/* ---- multi-GPU: heads sharded across one process per GPU --------------- */
+typedef struct qw_gpu_group qw_gpu_group;
+#define QW_GPU_GROUP_ID_BYTES 128
+/* Rank 0 creates the rendezvous id and hands the bytes to every rank by any
+ * host channel; each rank then joins with its own context. */
+int qw_gpu_group_new_id(void *id_bytes, char *error, size_t error_size);
+qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int world,
+                                char *error, size_t error_size);
+void qw_gpu_group_free(qw_gpu_group *group);
+int qw_gpu_group_rank(const qw_gpu_group *group);
+int qw_gpu_group_world(const qw_gpu_group *group);
+/* Gather the per-rank attention outputs [rows, heads_local*128] into the full
+ * [rows, world*heads_local*128] tensor on every rank (rank g owns head columns
+ * [g*heads_local, (g+1)*heads_local)).  Enqueued on the context's stream. */
+int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
+                                       const h3_gpu_tensor *local, uint32_t rows,
+                                       uint32_t heads_local, uint32_t head_dim);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

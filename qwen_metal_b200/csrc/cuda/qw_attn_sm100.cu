@@ -1,0 +1,791 @@
+// Block-causal (prefix-visible) flash-attention forward for sm_100a.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row sub-tiles that
+// ping-pong on the tensor pipe.  Q/K/V tiles arrive through TMA (128B swizzle)
+// into shared memory; S = Q K^T and O += P V run as tcgen05.mma with fp32
+// accumulators in tensor memory (TMEM); the softmax is fp32 in the exp2 domain,
+// one thread per query row, and writes P back to TMEM as bf16 over the S
+// columns so P V reads its A operand straight from TMEM.
+//
+// Warp roles (320 threads):
+//   warps 0-3  softmax + epilogue of sub-tile 0 (TMEM lanes 0..127)
+//   warps 4-7  softmax + epilogue of sub-tile 1
+//   warp  8    MMA issue (one elected lane), TMEM allocation
+//   warp  9    TMA producer (one elected lane)
+//
+// Mask: every row has an integer key limit (prefix) and the batch item may have
+// a key-padding window.  Key tiles past the largest limit of a sub-tile are
+// never issued, key tiles that lie completely inside the padding window are
+// skipped by all roles, interior tiles run without a compare, boundary tiles
+// apply the integer compare per element.
+//
+// Every wait is bounded: when one runs out the CTA records where in the status
+// words, raises a shared abort flag that all other waits poll, drains its TMA
+// loads, frees its TMEM and returns.
+//
+// Semantics follow the reference prefix kernel (h3_shaders.metal:3061-3272):
+// scale applied to fp32 scores, P rounded to bf16 before P V, fp32 accumulate,
+// output acc / l rounded to bf16; rows without a visible key store zeros.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../qw_cuda.h"
+
+namespace {
+
+constexpr int kHeadDim = 128;
+constexpr int kTileM = 128;  // query rows per sub-tile (= TMEM lanes)
+constexpr int kTileN = 128;  // keys per tile
+constexpr int kStages = 4;   // K/V ring slots
+constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32 KiB
+constexpr int kHalfTileBytes = kTileBytes / 2;     // one 64-column TMA box
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 384;
+// Lazy rescale threshold in the exp2 domain: P may grow to 2^8 before O and l
+// are brought back to the running maximum.
+constexpr float kRescaleThreshold = 8.0f;
+// Wait budget in SM clock cycles (~0.2 s); a healthy wait is microseconds.
+constexpr long long kWaitCycles = 400000000LL;
+
+enum Barrier : int {
+    kBarQFull = 0,                        // 2: Q sub-tile i landed
+    kBarKvFull = 2,                       // kStages
+    kBarKvEmpty = kBarKvFull + kStages,   // kStages
+    kBarSFull = kBarKvEmpty + kStages,    // 2: S_i complete in TMEM
+    kBarPFull = kBarSFull + 2,            // 2: P_i written (128 arrivals)
+    kBarOFinal = kBarPFull + 2,           // 2: last P V of sub-tile i complete
+    kBarCount = kBarOFinal + 2
+};
+
+struct __align__(16) SharedControl {
+    unsigned long long bars[kBarCount];
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+    int n_tiles[2];      // key tiles each sub-tile needs (by its largest limit)
+    int warp_max[8];     // per softmax warp: largest limit
+    int skip_lo, skip_hi;  // key tiles [skip_lo, skip_hi) lie inside the padding window
+};
+
+constexpr size_t kSmemData = (size_t)(2 + kStages) * kTileBytes;
+constexpr size_t kSmemBytes = kSmemData + sizeof(SharedControl) + 1024;  // +1024: manual alignment
+
+struct KernelParams {
+    __nv_bfloat16 *out;
+    const int32_t *kv_limit;
+    uint32_t *status;
+    int per_batch_limits;
+    int causal;
+    uint32_t causal_offset;
+    uint32_t batch, q_rows, kv_rows, heads, kv_heads;
+    uint32_t text_len[8];
+    uint32_t text_pad;
+    float scale_log2;  // scale * log2(e)
+    int head_major_out;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(unsigned long long *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false when the budget ran out here (recorded) or
+// another thread of the CTA already gave up.
+__device__ __noinline__ bool mbar_wait_slow(SharedControl *ctl, unsigned long long *bar,
+                                            uint32_t parity, uint32_t *status, uint32_t where,
+                                            uint32_t tile) {
+    long long start = clock64();
+    for (;;) {
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try(bar, parity)) return true;
+        if (ctl->abort_flag) return false;
+        if (clock64() - start > kWaitCycles) {
+            ctl->abort_flag = 1;
+            if (atomicCAS(status, 0u, (uint32_t)QWCU_STATUS_WAIT_TIMEOUT) == 0u) {
+                status[1] = where;
+                status[2] = tile;
+                status[3] = blockIdx.x | (blockIdx.y << 12) | (blockIdx.z << 24);
+            }
+            __threadfence();
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ bool mbar_wait(SharedControl *ctl, unsigned long long *bar,
+                                          uint32_t parity, uint32_t *status, uint32_t where,
+                                          uint32_t tile) {
+    if (mbar_try(bar, parity)) return true;
+    return mbar_wait_slow(ctl, bar, parity, status, where, tile);
+}
+
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map,
+                                            unsigned long long *bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_commit(unsigned long long *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     smem_u32(bar))
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): 128B swizzle, version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, M = 128, N = 128.
+constexpr uint32_t make_idesc(bool b_mn_major) {
+    return (1u << 4)                      // D format: f32
+           | (1u << 7)                    // A format: bf16
+           | (1u << 10)                   // B format: bf16
+           | ((b_mn_major ? 1u : 0u) << 16)
+           | ((uint32_t)(kTileN >> 3) << 17)
+           | ((uint32_t)(kTileM >> 4) << 24);
+}
+constexpr uint32_t kIdescQK = make_idesc(false);
+constexpr uint32_t kIdescPV = make_idesc(true);
+
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+#define QW_TMEM_LD32(taddr, r)                                                                  \
+    asm volatile(                                                                               \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                               \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "              \
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "    \
+        "[%32];"                                                                                \
+        : "=r"((r)[0]), "=r"((r)[1]), "=r"((r)[2]), "=r"((r)[3]), "=r"((r)[4]), "=r"((r)[5]),   \
+          "=r"((r)[6]), "=r"((r)[7]), "=r"((r)[8]), "=r"((r)[9]), "=r"((r)[10]), "=r"((r)[11]), \
+          "=r"((r)[12]), "=r"((r)[13]), "=r"((r)[14]), "=r"((r)[15]), "=r"((r)[16]),            \
+          "=r"((r)[17]), "=r"((r)[18]), "=r"((r)[19]), "=r"((r)[20]), "=r"((r)[21]),            \
+          "=r"((r)[22]), "=r"((r)[23]), "=r"((r)[24]), "=r"((r)[25]), "=r"((r)[26]),            \
+          "=r"((r)[27]), "=r"((r)[28]), "=r"((r)[29]), "=r"((r)[30]), "=r"((r)[31])             \
+        : "r"(taddr))
+
+#define QW_TMEM_ST32(taddr, r)                                                                  \
+    asm volatile(                                                                               \
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "                                         \
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "             \
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"     \
+        ::"r"(taddr), "r"((r)[0]), "r"((r)[1]), "r"((r)[2]), "r"((r)[3]), "r"((r)[4]),          \
+          "r"((r)[5]), "r"((r)[6]), "r"((r)[7]), "r"((r)[8]), "r"((r)[9]), "r"((r)[10]),        \
+          "r"((r)[11]), "r"((r)[12]), "r"((r)[13]), "r"((r)[14]), "r"((r)[15]), "r"((r)[16]),   \
+          "r"((r)[17]), "r"((r)[18]), "r"((r)[19]), "r"((r)[20]), "r"((r)[21]), "r"((r)[22]),   \
+          "r"((r)[23]), "r"((r)[24]), "r"((r)[25]), "r"((r)[26]), "r"((r)[27]), "r"((r)[28]),   \
+          "r"((r)[29]), "r"((r)[30]), "r"((r)[31])                                              \
+        : "memory")
+
+__device__ __forceinline__ void tmem_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ int row_limit(const KernelParams &p, uint32_t b, uint32_t r) {
+    if (r >= p.q_rows) return 0;
+    if (p.text_pad && r >= p.text_len[b] && r < p.text_pad) return 0;  // padding query row
+    int limit;
+    if (p.kv_limit) {
+        limit = p.kv_limit[p.per_batch_limits ? (size_t)b * p.q_rows + r : r];
+        limit = max(limit, 0);
+    } else if (p.causal) {
+        unsigned long long c = (unsigned long long)r + 1ull + p.causal_offset;
+        limit = (int)min(c, (unsigned long long)p.kv_rows);
+    } else {
+        limit = (int)p.kv_rows;
+    }
+    return min(limit, (int)p.kv_rows);
+}
+
+__device__ __forceinline__ bool tile_skipped(const SharedControl *ctl, int j) {
+    return j >= ctl->skip_lo && j < ctl->skip_hi;
+}
+
+// ---------------------------------------------------------------------------
+// Softmax + epilogue role: 128 threads per sub-tile, one query row each.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void softmax_role(const KernelParams &p, SharedControl *ctl,
+                                             int sub, int tid_in_group, int my_limit, uint32_t b,
+                                             uint32_t h, uint32_t row) {
+    const int warp_in_group = tid_in_group >> 5;
+    const uint32_t lane_base = (uint32_t)(warp_in_group * 32) << 16;
+    const uint32_t tmem = ctl->tmem_base;
+    const uint32_t tmem_s = tmem + lane_base + (sub ? kTmemS1 : kTmemS0);
+    const uint32_t tmem_o = tmem + lane_base + (sub ? kTmemO1 : kTmemO0);
+    unsigned long long *bar_s = &ctl->bars[kBarSFull + sub];
+    unsigned long long *bar_p = &ctl->bars[kBarPFull + sub];
+    const int n_tiles = ctl->n_tiles[sub];
+    const int pad_lo = p.text_pad ? (int)p.text_len[b] : 0;
+    const int pad_hi = (int)p.text_pad;
+    const float c = p.scale_log2;
+    const bool neg = c < 0.0f;
+
+    float m_run = -INFINITY;  // running extreme of the raw scores (max, or min when c < 0)
+    float m_ref = -INFINITY;  // extreme the stored exponents refer to
+    float l_run = 0.0f;
+    uint32_t phase = 0;
+    bool ok = true;
+    int processed = 0;
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+        if (tile_skipped(ctl, j)) continue;
+        ok = mbar_wait(ctl, bar_s, phase, p.status, (1u << 16) | (uint32_t)(kBarSFull + sub),
+                       (uint32_t)j);
+        if (!ok) break;
+        phase ^= 1u;
+        tc_fence_after();
+
+        uint32_t s[128];
+        QW_TMEM_LD32(tmem_s + 0, s + 0);
+        QW_TMEM_LD32(tmem_s + 32, s + 32);
+        QW_TMEM_LD32(tmem_s + 64, s + 64);
+        QW_TMEM_LD32(tmem_s + 96, s + 96);
+        tmem_wait_ld();
+
+        const int key0 = j * kTileN;
+        const bool pad_hit = pad_hi > pad_lo && key0 < pad_hi && key0 + kTileN > pad_lo;
+        const bool boundary = __any_sync(0xffffffffu, key0 + kTileN > my_limit) || pad_hit;
+        const float sign = neg ? -1.0f : 1.0f;
+        if (boundary) {
+#pragma unroll
+            for (int i = 0; i < 128; ++i) {
+                int key = key0 + i;
+                bool visible = key < my_limit && !(key >= pad_lo && key < pad_hi);
+                s[i] = visible ? s[i] : __float_as_uint(neg ? INFINITY : -INFINITY);
+            }
+        }
+        // Row extreme of sign*score (four independent chains).
+        float e0 = -INFINITY, e1 = -INFINITY, e2 = -INFINITY, e3 = -INFINITY;
+        if (!neg) {
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                e0 = fmaxf(e0, __uint_as_float(s[i]));
+                e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
+                e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
+                e3 = fmaxf(e3, __uint_as_float(s[i + 3]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                e0 = fmaxf(e0, -__uint_as_float(s[i]));
+                e1 = fmaxf(e1, -__uint_as_float(s[i + 1]));
+                e2 = fmaxf(e2, -__uint_as_float(s[i + 2]));
+                e3 = fmaxf(e3, -__uint_as_float(s[i + 3]));
+            }
+        }
+        const float m_tile = fmaxf(fmaxf(e0, e1), fmaxf(e2, e3));  // in sign*score units
+        const float m_new = fmaxf(m_run, m_tile);
+        m_run = m_new;
+        const float ac = fabsf(c);
+        // Does the reference point have to move?  (first finite value, or drift > threshold)
+        const bool move = (m_new != -INFINITY) &&
+                          (m_ref == -INFINITY || (m_new - m_ref) * ac > kRescaleThreshold);
+        const bool any_move = __any_sync(0xffffffffu, move && processed > 0 && m_ref != -INFINITY);
+        float alpha = 1.0f;
+        if (move) {
+            alpha = (m_ref == -INFINITY) ? 0.0f : fast_exp2((m_ref - m_new) * ac);
+            m_ref = m_new;
+        }
+        if (any_move) {
+            // s_full of this tile was committed after the previous P V of this
+            // sub-tile, so O is quiescent until P of this tile is published.
+#pragma unroll 1
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                uint32_t o[32];
+                QW_TMEM_LD32(tmem_o + chunk * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                QW_TMEM_ST32(tmem_o + chunk * 32, o);
+            }
+            tmem_wait_st();
+        }
+        l_run *= alpha;
+
+        // P = exp2(sign*score*|c| - m_ref*|c|) as bf16 pairs, written over S.
+        const float bias = (m_ref == -INFINITY) ? 0.0f : -m_ref * ac;
+        const float cs = sign * ac;
+        uint32_t pk[64];
+        float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 128; i += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), cs, bias));
+            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), cs, bias));
+            sum0 += p0;
+            sum1 += p1;
+            pk[i >> 1] = pack_bf16(p0, p1);
+        }
+        QW_TMEM_ST32(tmem_s + 0, pk + 0);
+        QW_TMEM_ST32(tmem_s + 32, pk + 32);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p);
+        l_run += sum0 + sum1;
+        ++processed;
+    }
+
+    // Epilogue: O / l -> bf16 -> global (this thread's row of this head).
+    __nv_bfloat16 *dst = nullptr;
+    if (row < p.q_rows) {
+        size_t index = p.head_major_out
+                           ? (((size_t)b * p.heads + h) * p.q_rows + row) * kHeadDim
+                           : (((size_t)b * p.q_rows + row) * p.heads + h) * kHeadDim;
+        dst = p.out + index;
+    }
+    if (processed == 0 || !ok) {
+        if (dst && ok) {
+            uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) reinterpret_cast<uint4 *>(dst)[i] = zero;
+        }
+        return;
+    }
+    ok = mbar_wait(ctl, &ctl->bars[kBarOFinal + sub], 0, p.status,
+                   (1u << 16) | (uint32_t)(kBarOFinal + sub), 0xffffu);
+    if (!ok) return;
+    tc_fence_after();
+    const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll 1
+    for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t o[32];
+        QW_TMEM_LD32(tmem_o + chunk * 32, o);
+        tmem_wait_ld();
+        if (dst) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                reinterpret_cast<uint4 *>(dst + chunk * 32)[i >> 3] = v;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// MMA issue role (one thread).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_addr, uint32_t k_addr) {
+    // K-major operands, 128B swizzle: 8-row groups 1024 B apart; the second
+    // 64-column box sits one half tile further; 16 columns = 32 B per step.
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        uint32_t off = (uint32_t)(kk >> 2) * kHalfTileBytes + (uint32_t)(kk & 3) * 32u;
+        mma_ss(d_tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024),
+               kIdescQK, kk > 0 ? 1u : 0u);
+    }
+}
+
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_addr,
+                                         bool accumulate) {
+    // A = P from TMEM (16 keys = 8 packed columns per step).  B = V, MN-major:
+    // 16 keys = 2 groups of 8 rows (1024 B apart), the two 64-wide column
+    // halves one half tile apart.
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        mma_ts(d_tmem, p_tmem + (uint32_t)kk * 8u,
+               smem_desc(v_addr + (uint32_t)kk * 2048u, kHalfTileBytes, 1024), kIdescPV,
+               (accumulate || kk > 0) ? 1u : 0u);
+    }
+}
+
+__device__ __forceinline__ int next_tile(const SharedControl *ctl, int j, int n_max) {
+    ++j;
+    if (j >= ctl->skip_lo && j < ctl->skip_hi) j = ctl->skip_hi;
+    return j < n_max ? j : n_max;
+}
+
+__device__ void mma_role(const KernelParams &p, SharedControl *ctl, uint8_t *smem_q,
+                         uint8_t *smem_kv) {
+    const int n0 = ctl->n_tiles[0], n1 = ctl->n_tiles[1];
+    const int n_max = max(n0, n1);
+    int j = next_tile(ctl, -1, n_max);
+    if (j >= n_max) return;
+    const uint32_t tmem = ctl->tmem_base;
+    const uint32_t q_addr[2] = {smem_u32(smem_q), smem_u32(smem_q + kTileBytes)};
+    const uint32_t s_tmem[2] = {tmem + kTmemS0, tmem + kTmemS1};
+    const uint32_t o_tmem[2] = {tmem + kTmemO0, tmem + kTmemO1};
+    const int n_sub[2] = {n0, n1};
+    uint32_t p_phase[2] = {0, 0};
+    bool o_started[2] = {false, false};
+    uint32_t t = 0;  // ring position (K and V tiles alternate)
+    const uint32_t where = 2u << 16;
+
+    for (int i = 0; i < 2; ++i)
+        if (n_sub[i] > 0 &&
+            !mbar_wait(ctl, &ctl->bars[kBarQFull + i], 0, p.status, where | (kBarQFull + i), 0))
+            return;
+    {
+        uint32_t slot = t % kStages, par = (t / kStages) & 1u;
+        ++t;
+        if (!mbar_wait(ctl, &ctl->bars[kBarKvFull + slot], par, p.status,
+                       where | (kBarKvFull + slot), (uint32_t)j))
+            return;
+        tc_fence_after();
+        uint32_t k_addr = smem_u32(smem_kv + (size_t)slot * kTileBytes);
+        for (int i = 0; i < 2; ++i)
+            if (j < n_sub[i]) {
+                issue_qk(s_tmem[i], q_addr[i], k_addr);
+                tc_commit(&ctl->bars[kBarSFull + i]);
+            }
+        tc_commit(&ctl->bars[kBarKvEmpty + slot]);
+    }
+    while (j < n_max) {
+        const int jn = next_tile(ctl, j, n_max);
+        uint32_t v_slot = t % kStages, v_par = (t / kStages) & 1u;
+        ++t;
+        uint32_t k_slot = 0, k_par = 0;
+        if (jn < n_max) {
+            k_slot = t % kStages;
+            k_par = (t / kStages) & 1u;
+            ++t;
+        }
+        if (!mbar_wait(ctl, &ctl->bars[kBarKvFull + v_slot], v_par, p.status,
+                       where | (kBarKvFull + v_slot), (uint32_t)j))
+            return;
+        const uint32_t v_addr = smem_u32(smem_kv + (size_t)v_slot * kTileBytes);
+        const uint32_t k_addr = smem_u32(smem_kv + (size_t)k_slot * kTileBytes);
+        bool k_ready = false;
+        for (int i = 0; i < 2; ++i) {
+            if (j < n_sub[i]) {
+                if (!mbar_wait(ctl, &ctl->bars[kBarPFull + i], p_phase[i], p.status,
+                               where | (kBarPFull + i), (uint32_t)j))
+                    return;
+                p_phase[i] ^= 1u;
+                tc_fence_after();
+                issue_pv(o_tmem[i], s_tmem[i], v_addr, o_started[i]);
+                o_started[i] = true;
+            }
+            if (i == 1) tc_commit(&ctl->bars[kBarKvEmpty + v_slot]);
+            if (jn < n_max && jn < n_sub[i]) {
+                if (!k_ready) {
+                    if (!mbar_wait(ctl, &ctl->bars[kBarKvFull + k_slot], k_par, p.status,
+                                   where | (kBarKvFull + k_slot), (uint32_t)jn))
+                        return;
+                    tc_fence_after();
+                    k_ready = true;
+                }
+                issue_qk(s_tmem[i], q_addr[i], k_addr);
+                tc_commit(&ctl->bars[kBarSFull + i]);
+            }
+        }
+        if (jn < n_max) {
+            if (!k_ready &&
+                !mbar_wait(ctl, &ctl->bars[kBarKvFull + k_slot], k_par, p.status,
+                           where | (kBarKvFull + k_slot), (uint32_t)jn))
+                return;
+            tc_commit(&ctl->bars[kBarKvEmpty + k_slot]);
+        }
+        j = jn;
+    }
+    tc_commit(&ctl->bars[kBarOFinal + 0]);
+    tc_commit(&ctl->bars[kBarOFinal + 1]);
+}
+
+// ---------------------------------------------------------------------------
+// TMA producer role (one thread).
+// ---------------------------------------------------------------------------
+__device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *smem_kv,
+                         const CUtensorMap *map_k, const CUtensorMap *map_v, uint32_t b,
+                         uint32_t kvh) {
+    const int n_max = max(ctl->n_tiles[0], ctl->n_tiles[1]);
+    const uint32_t where = 3u << 16;
+    uint32_t t = 0;
+    bool ok = true;
+    for (int j = next_tile(ctl, -1, n_max); j < n_max && ok; j = next_tile(ctl, j, n_max)) {
+        for (int which = 0; which < 2 && ok; ++which) {
+            uint32_t slot = t % kStages, par = ((t / kStages) & 1u) ^ 1u;
+            ok = mbar_wait(ctl, &ctl->bars[kBarKvEmpty + slot], par, p.status,
+                           where | (kBarKvEmpty + slot), (uint32_t)j);
+            if (!ok) break;
+            ++t;
+            uint8_t *dst = smem_kv + (size_t)slot * kTileBytes;
+            unsigned long long *bar = &ctl->bars[kBarKvFull + slot];
+            mbar_expect_tx(bar, kTileBytes);
+            const CUtensorMap *map = which ? map_v : map_k;
+            int col = (int)(kvh * kHeadDim);
+            tma_load_3d(dst, map, bar, col, j * kTileN, (int)b);
+            tma_load_3d(dst + kHalfTileBytes, map, bar, col + 64, j * kTileN, (int)b);
+        }
+    }
+    // Leave no copy in flight: every issued load must have landed before the
+    // CTA may release its shared memory (bounded like every other wait).
+    uint32_t first = t > (uint32_t)kStages ? t - kStages : 0;
+    for (uint32_t u = first; u < t; ++u) {
+        uint32_t slot = u % kStages, par = (u / kStages) & 1u;
+        long long start = clock64();
+        while (!mbar_try(&ctl->bars[kBarKvFull + slot], par))
+            if (clock64() - start > kWaitCycles) break;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
+                     const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const KernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *smem_q = smem;
+    uint8_t *smem_kv = smem + 2 * kTileBytes;
+    SharedControl *ctl = reinterpret_cast<SharedControl *>(smem + kSmemData);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const uint32_t b = blockIdx.z;
+    const uint32_t h = blockIdx.y;
+    const uint32_t kvh = (uint32_t)((unsigned long long)h * p.kv_heads / p.heads);
+    // Heaviest query blocks first: rows late in the joint sequence see the most keys.
+    const uint32_t qblock = gridDim.x - 1 - blockIdx.x;
+    const uint32_t row0 = qblock * (2 * kTileM);
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) mbar_init(&ctl->bars[kBarQFull + i], 1);
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&ctl->bars[kBarKvFull + i], 1);
+            mbar_init(&ctl->bars[kBarKvEmpty + i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&ctl->bars[kBarSFull + i], 1);
+            mbar_init(&ctl->bars[kBarPFull + i], kTileM);
+            mbar_init(&ctl->bars[kBarOFinal + i], 1);
+        }
+        ctl->abort_flag = 0;
+        int lo = 0, hi = 0;
+        if (p.text_pad && p.text_len[b] < p.text_pad) {
+            lo = ((int)p.text_len[b] + kTileN - 1) / kTileN;
+            hi = (int)p.text_pad / kTileN;
+            if (hi < lo) hi = lo;
+        }
+        ctl->skip_lo = lo;
+        ctl->skip_hi = hi;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&ctl->tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
+    // Row limits: each softmax thread owns one row; the largest limit of a
+    // sub-tile bounds its key-tile loop.
+    int my_limit = 0;
+    uint32_t my_row = 0;
+    int sub = 0, tid_in_group = 0;
+    if (tid < kSoftmaxThreads) {
+        sub = tid >> 7;
+        tid_in_group = tid & 127;
+        my_row = row0 + (uint32_t)sub * kTileM + (uint32_t)tid_in_group;
+        my_limit = row_limit(p, b, my_row);
+        int warp_max = my_limit;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1)
+            warp_max = max(warp_max, __shfl_xor_sync(0xffffffffu, warp_max, off));
+        if (lane == 0) ctl->warp_max[warp] = warp_max;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (tid < 2) {
+        int m = 0;
+        for (int w = 0; w < 4; ++w) m = max(m, ctl->warp_max[tid * 4 + w]);
+        ctl->n_tiles[tid] = (m + kTileN - 1) / kTileN;
+    }
+    // Q does not depend on the limits: start it before the second barrier.
+    if (warp == kTmaWarp && lane == 0) {
+        for (int i = 0; i < 2; ++i) {
+            uint32_t r = row0 + (uint32_t)i * kTileM;
+            if (r >= p.q_rows) continue;  // inactive sub-tile: n_tiles is 0, nobody waits
+            unsigned long long *bar = &ctl->bars[kBarQFull + i];
+            mbar_expect_tx(bar, kTileBytes);
+            uint8_t *dst = smem_q + (size_t)i * kTileBytes;
+            tma_load_3d(dst, &map_q, bar, (int)(h * kHeadDim), (int)r, (int)b);
+            tma_load_3d(dst + kHalfTileBytes, &map_q, bar, (int)(h * kHeadDim) + 64, (int)r, (int)b);
+        }
+    }
+    __syncthreads();
+
+    if (tid < kSoftmaxThreads) {
+        softmax_role(p, ctl, sub, tid_in_group, my_limit, b, h, my_row);
+    } else if (warp == kMmaWarp) {
+        if (lane == 0) mma_role(p, ctl, smem_q, smem_kv);
+    } else if (lane == 0) {
+        tma_role(p, ctl, smem_kv, &map_k, &map_v, b, kvh);
+        // Q loads of active sub-tiles must have landed as well.
+        for (int i = 0; i < 2; ++i) {
+            if (row0 + (uint32_t)i * kTileM >= p.q_rows) continue;
+            long long start = clock64();
+            while (!mbar_try(&ctl->bars[kBarQFull + i], 0))
+                if (clock64() - start > kWaitCycles) break;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(ctl->tmem_base),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// [batch][rows][heads*128] bf16, boxes of 128 rows x 64 columns, 128B swizzle.
+int make_map(CUtensorMap *map, const void *base, uint32_t batch, uint32_t rows, uint32_t heads) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[3] = {(cuuint64_t)heads * kHeadDim, rows, batch};
+    cuuint64_t strides[2] = {(cuuint64_t)heads * kHeadDim * 2,
+                             (cuuint64_t)rows * heads * kHeadDim * 2};
+    cuuint32_t box[3] = {64, kTileN, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void *>(base), dims,
+                    strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (a->batch == 0 || a->batch > 8 || !a->q_rows || !a->kv_rows || !a->heads || !a->kv_heads)
+        return (int)cudaErrorInvalidValue;
+    // TMA needs 16-byte aligned bases; cudaMalloc gives 256.
+    if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15u)
+        return (int)cudaErrorMisalignedAddress;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(qw_attn_sm100_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    CUtensorMap map_q, map_k, map_v;
+    int rc;
+    if ((rc = make_map(&map_q, a->q, a->batch, a->q_rows, a->heads))) return rc;
+    if ((rc = make_map(&map_k, a->k, a->batch, a->kv_rows, a->kv_heads))) return rc;
+    if ((rc = make_map(&map_v, a->v, a->batch, a->kv_rows, a->kv_heads))) return rc;
+    KernelParams p;
+    p.out = static_cast<__nv_bfloat16 *>(a->out);
+    p.kv_limit = a->kv_limit;
+    p.status = a->status;
+    p.per_batch_limits = a->per_batch_limits;
+    p.causal = a->causal;
+    p.causal_offset = a->causal_offset;
+    p.batch = a->batch;
+    p.q_rows = a->q_rows;
+    p.kv_rows = a->kv_rows;
+    p.heads = a->heads;
+    p.kv_heads = a->kv_heads;
+    for (int i = 0; i < 8; ++i) p.text_len[i] = a->text_len[i];
+    p.text_pad = a->text_pad;
+    p.scale_log2 = a->scale * 1.4426950408889634f;
+    p.head_major_out = a->head_major_out;
+    dim3 grid((a->q_rows + 2 * kTileM - 1) / (2 * kTileM), a->heads, a->batch);
+    qw_attn_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    return (int)cudaGetLastError();
+}

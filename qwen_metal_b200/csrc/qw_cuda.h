@@ -1,0 +1,112 @@
+/* Thin extern-"C" CUDA layer under the C11 host code.
+ *
+ * The host side (h3_context.c, qw_ops.c) validates arguments the way the
+ * reference's op wrappers do and then calls one of these launchers with raw
+ * device pointers.  Every launcher only enqueues work on `stream` and returns
+ * 0 on success or a CUDA error code; device-side failures (a bounded wait
+ * that ran out) are recorded in the `status` words and surface at submit.
+ */
+#ifndef QW_CUDA_H
+#define QW_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque here so C11 translation units need no CUDA headers. */
+typedef void *qwcu_stream;
+
+enum {
+    QWCU_STATUS_OK = 0,
+    QWCU_STATUS_WAIT_TIMEOUT = 1, /* status[1] = role<<16 | barrier id, status[2] = tile */
+    QWCU_STATUS_BAD_ARGUMENT = 2
+};
+#define QWCU_STATUS_WORDS 8
+
+/* Geometry + mask description shared by every attention kernel.
+ *
+ * Layouts (elements are bf16):
+ *   q   [batch][q_rows ][heads   ][128]
+ *   k,v [batch][kv_rows][kv_heads][128]
+ *   out [batch][q_rows ][heads   ][128], or [batch][heads][q_rows][128] when
+ *       head_major_out != 0.
+ * Visible keys of (batch b, row r): s < limit(b,r), minus the key-padding
+ * window text_len[b] <= s < text_pad when text_pad != 0.  limit(b,r) is
+ *   kv_limit != NULL : clamp((int32)kv_limit[per_batch ? b*q_rows+r : r], 0, kv_rows)
+ *   causal != 0      : min(r + 1 + causal_offset, kv_rows)
+ *   otherwise        : kv_rows.
+ * Query rows inside the padding window and rows with no visible key store zeros.
+ */
+typedef struct {
+    const void *q;
+    const void *k;
+    const void *v;
+    void *out;
+    const int32_t *kv_limit;
+    int per_batch_limits;
+    int causal;
+    uint32_t causal_offset;
+    uint32_t batch;
+    uint32_t q_rows;
+    uint32_t kv_rows;
+    uint32_t heads;
+    uint32_t kv_heads;
+    uint32_t text_len[8]; /* per batch item; used when text_pad != 0 (batch <= 8) */
+    uint32_t text_pad;
+    float scale;
+    int scale_in_q; /* h3 causal variant: q' = bf16(q*scale), scores unscaled */
+    int head_major_out;
+    uint32_t *status; /* QWCU_STATUS_WORDS device words, zero when healthy */
+} qwcu_attn_args;
+
+/* tcgen05/TMEM/TMA flash-attention forward (sm_100a). */
+int qwcu_attn_sm100_launch(const qwcu_attn_args *args, qwcu_stream stream);
+/* One-warp-per-(row, head) fp32 kernel; the diagnostic cross-check path. */
+int qwcu_attn_scalar_launch(const qwcu_attn_args *args, qwcu_stream stream);
+
+/* Fused per-head RMSNorm + interleaved RoPE over q and k, in place or out of
+ * place.  Any of the stages can be switched off so the three legacy entry
+ * points share the same device code:
+ *   norm_weight_q/k == NULL -> no norm for that tensor
+ *   rope_cos == NULL        -> no rotation
+ *   k_in == NULL            -> only q is processed
+ * double_round selects bf16(bf16(x*inv)*w). */
+typedef struct {
+    const void *q_in;
+    const void *k_in;
+    void *q_out;
+    void *k_out;
+    const void *norm_weight_q;
+    const void *norm_weight_k;
+    const float *rope_cos;
+    const float *rope_sin;
+    uint32_t rows; /* batch*sequence rows of [heads][128] */
+    uint32_t table_rows; /* rope row = row % table_rows (batch items share tables) */
+    uint32_t heads;
+    float epsilon;
+    int double_round;
+} qwcu_prologue_args;
+
+int qwcu_prologue_launch(const qwcu_prologue_args *args, qwcu_stream stream);
+
+/* h3 causal variant helper: out = bf16(in * scale), elementwise. */
+int qwcu_scale_bf16_launch(void *out, const void *in, size_t elements, float scale,
+                           qwcu_stream stream);
+
+/* Multi-GPU gather epilogue: staged [world][rows][slice] -> full [rows][world*slice]
+ * (bf16 elements; slice_elements must be a multiple of 8). */
+int qwcu_interleave_launch(void *full, const void *staged, uint32_t rows,
+                           uint32_t slice_elements, uint32_t world, int sm_count,
+                           qwcu_stream stream);
+
+/* Device properties needed by the host side. */
+int qwcu_device_sm_count(int device);
+int qwcu_device_cc(int device); /* major*10 + minor */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

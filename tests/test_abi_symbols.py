@@ -1,0 +1,65 @@
+"""CPU: the shared library loads without a GPU and exports every symbol the
+headers under include/ declare; the ctypes stub covers the same set."""
+import ctypes
+import glob
+import os
+import re
+
+import pytest
+
+from qwen_metal_b200 import abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    names = set()
+    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = open(path).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        for m in re.finditer(r"\b((?:h3_gpu|qw)_\w+)\s*\(", text):
+            names.add(m.group(1))
+    return sorted(names)
+
+
+def test_headers_declare_the_hot_path():
+    names = declared_functions()
+    for required in ("h3_gpu_create", "h3_gpu_submit", "h3_gpu_head_rms_norm_bf16",
+                     "qw_gpu_qk_rope_bf16", "qw_gpu_flash_sdpa_prefix_bf16",
+                     "qw_gpu_flash_sdpa_bf16", "qw_gpu_sdpa_rect_bf16", "qw_gpu_gqa_causal_bf16",
+                     "h3_gpu_gqa_causal_bf16", "h3_gpu_sdpa_bf16", "qw_dit_prefix_limits",
+                     "qw_pipe_rope_tables", "qw_gpu_qk_norm_rope_bf16",
+                     "qw_gpu_attn_block_causal_bf16"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(abi.LIB_PATH)
+    missing = [n for n in declared_functions() if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_ctypes_stub_covers_the_headers():
+    assert sorted(abi.exported_names()) == declared_functions()
+
+
+def test_create_without_gpu_fails_loudly_or_succeeds():
+    """No CPU fallback: without a device, create returns NULL and says why."""
+    lib = abi.load()
+    err = ctypes.create_string_buffer(512)
+    handle = lib.h3_gpu_create(b"h3_shaders.metal", err, len(err))
+    if handle:
+        lib.h3_gpu_free(handle)
+    else:
+        assert b"no CPU path" in err.value or b"sm_100a" in err.value
+
+
+def test_null_handles_are_safe():
+    lib = abi.load()
+    lib.h3_gpu_free(None)
+    lib.h3_gpu_tensor_free(None)
+    assert lib.h3_gpu_tensor_elements(None) == 0
+    assert lib.h3_gpu_begin(None) == 0
+    assert lib.h3_gpu_submit(None) == 0
+    assert lib.h3_gpu_error(None) is not None
+    assert lib.h3_gpu_is_m5(None) == 0

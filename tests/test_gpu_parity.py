@@ -1,0 +1,454 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle
+on identical seeded inputs.
+
+Gates on bf16 outputs (stated once here, used everywhere):
+  max-abs <= 2e-2 and mean-abs <= 2e-3 (benchmark definition) and
+  relL2   <  5e-3 (the reference's own gate, tests/test_prefix_kernel.c:140-142).
+Integer work (limits, mask indexing) is checked bit-exactly.
+"""
+import ctypes as C
+import math
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from qwen_metal_b200 import abi, workloads
+from qwen_metal_b200.abi import bf16_to_f32, f32_to_bf16
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+MAX_ABS, MEAN_ABS, REL_L2 = 2e-2, 2e-3, 5e-3
+SCALE = workloads.SCALE
+
+
+def gates(got_bits, ref_f32, what=""):
+    got = bf16_to_f32(np.asarray(got_bits)).astype(np.float64).ravel()
+    ref = np.asarray(ref_f32, dtype=np.float64).ravel()
+    assert np.isfinite(got).all(), f"{what}: non-finite output"
+    diff = np.abs(got - ref)
+    rel = math.sqrt((diff ** 2).sum() / max((ref ** 2).sum(), 1e-30))
+    assert diff.max() <= MAX_ABS, f"{what}: max-abs {diff.max():.3e}"
+    assert diff.mean() <= MEAN_ABS, f"{what}: mean-abs {diff.mean():.3e}"
+    assert rel < REL_L2, f"{what}: relL2 {rel:.3e}"
+    return diff.max(), diff.mean(), rel
+
+
+def randn_bf16(rng, shape, mean=0.0, std=1.0):
+    return workloads.normal_bf16(rng, shape, mean, std)
+
+
+def run_prefix(gpu, q, k, v, limits, q_rows, kv_rows, heads, kv_heads, scale=SCALE, q_alloc=None):
+    lib = gpu.lib
+    qt = gpu.bf16(q if q_alloc is None else np.concatenate(
+        [q.ravel(), np.full(q_alloc - q.size, 0x7FC0, np.uint16)]))  # NaN padding rows
+    kt, vt = gpu.bf16(k), gpu.bf16(v)
+    ot = gpu.new_bf16(q_rows * heads * 128)
+    lt = gpu.u32(limits)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_flash_sdpa_prefix_bf16(gpu.handle, ot, qt, kt, vt, lt, q_rows, kv_rows,
+                                                heads, kv_heads, 128, scale), "prefix")
+    gpu.submit()
+    out = gpu.read_bf16(ot, q_rows * heads * 128)
+    for t in (qt, kt, vt, ot, lt):
+        gpu.free(t)
+    return out.reshape(q_rows, heads, 128)
+
+
+@pytest.fixture(params=["sm100", "scalar"])
+def kernel(request, gpu):
+    assert gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, request.param.encode())
+    yield request.param
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+
+
+# --------------------------------------------------------------------------
+# config 0: the reference's own known-answer test
+# --------------------------------------------------------------------------
+def test_cfg0_reference_kat(gpu, kernel):
+    q, k, v, limits = O.kat_inputs()
+    ref, _ = O.sdpa(q, k, v, limits, 1, 149, 149, 32, 32, SCALE)
+    # the reference over-allocates Q to a multiple of 64 rows (test_prefix_kernel.c:99-101)
+    out = run_prefix(gpu, q, k, v, limits, 149, 149, 32, 32, q_alloc=192 * 32 * 128)
+    gates(out, ref[0], f"cfg0/{kernel}")
+
+
+def test_cfg0_reference_test_binary(gpu):
+    """tests/test_prefix_kernel.c compiled unmodified against this library
+    (built where a reference checkout exists; the binary travels with the tree)."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "test_prefix_kernel_cuda")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/test_prefix_kernel_cuda not built")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert "PASS" in res.stdout, res.stdout + res.stderr
+
+
+# --------------------------------------------------------------------------
+# prologue
+# --------------------------------------------------------------------------
+def ulp_distance(a_bits, b_bits):
+    """Distance in bf16 steps between two bf16 bit patterns (sign-magnitude order)."""
+    def key(x):
+        x = x.astype(np.int32)
+        return np.where(x & 0x8000, -(x & 0x7FFF), x & 0x7FFF)
+    return np.abs(key(a_bits) - key(b_bits))
+
+
+def test_prologue_legacy_entry_points(gpu):
+    rng = np.random.default_rng(11)
+    S, H = 149, 24
+    lib = gpu.lib
+    x = randn_bf16(rng, (S, H, 128))
+    w = randn_bf16(rng, (128,), 1.0, 0.1)
+    for fn, dbl in ((lib.h3_gpu_head_rms_norm_bf16, False), (lib.qw_gpu_head_rms_norm_bf16, True)):
+        t, wt = gpu.bf16(x), gpu.bf16(w)
+        gpu.begin()
+        gpu.check(fn(gpu.handle, t, wt, S, H, 128, 1e-6), "head norm")
+        gpu.submit()
+        got = gpu.read_bf16(t, x.size).reshape(x.shape)
+        ref = O.head_rms_norm(x, w, S, H, 1e-6, dbl)
+        d = ulp_distance(got, ref)
+        assert d.max() <= 1, d.max()               # warp-tree vs serial sum: rare 1-ulp flips
+        assert (d > 0).mean() < 2e-3, (d > 0).mean()
+        gpu.free(t), gpu.free(wt)
+    cos, sin = abi.rope_tables(21, 8, 16)
+    k = randn_bf16(rng, (S, H, 128))
+    qt, kt, ct, st = gpu.bf16(x), gpu.bf16(k), gpu.f32(cos), gpu.f32(sin)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_qk_rope_bf16(gpu.handle, qt, kt, qt, kt, ct, st, S, H, 128), "rope")
+    gpu.submit()
+    rq, rk = O.qk_rope(x, k, cos, sin, S, H)
+    assert np.array_equal(gpu.read_bf16(qt, x.size).reshape(x.shape), rq)   # bit-exact
+    assert np.array_equal(gpu.read_bf16(kt, k.size).reshape(k.shape), rk)
+    for t in (qt, kt, ct, st):
+        gpu.free(t)
+
+
+def prologue_oracle(q, k, wq, wk, cos, sin, batch, rows, heads):
+    qn = O.head_rms_norm(q, wq, batch * rows, heads, 1e-6)
+    kn = O.head_rms_norm(k, wk, batch * rows, heads, 1e-6)
+    qo, ko = np.empty_like(qn), np.empty_like(kn)
+    for b in range(batch):
+        qo[b], ko[b] = O.qk_rope(qn[b], kn[b], cos, sin, rows, heads)
+    return qo, ko
+
+
+def test_prologue_fused_matches_three_kernel_sequence(gpu):
+    w = workloads.workload(2)
+    q, k, v, wq, wk = workloads.layer_inputs(w, 0)
+    cos, sin = w.rope_tables()
+    qt, kt, wqt, wkt = gpu.bf16(q), gpu.bf16(k), gpu.bf16(wq), gpu.bf16(wk)
+    ct, st = gpu.f32(cos), gpu.f32(sin)
+    gpu.begin()
+    gpu.check(gpu.lib.qw_gpu_qk_norm_rope_bf16(gpu.handle, qt, kt, wqt, wkt, ct, st, w.batch,
+                                               w.rows, w.heads, 128, 1e-6), "fused prologue")
+    gpu.submit()
+    rq, rk = prologue_oracle(q, k, wq, wk, cos, sin, w.batch, w.rows, w.heads)
+    for got, ref in ((gpu.read_bf16(qt, q.size), rq), (gpu.read_bf16(kt, k.size), rk)):
+        d = ulp_distance(got.reshape(ref.shape), ref)
+        assert d.max() <= 1 and (d > 0).mean() < 2e-3, (d.max(), (d > 0).mean())
+    for t in (qt, kt, wqt, wkt, ct, st):
+        gpu.free(t)
+
+
+# --------------------------------------------------------------------------
+# configs 1, 2 in full; 3-5 on a deterministic row sample
+# --------------------------------------------------------------------------
+def sample_rows(w, count, seed=5):
+    """Rows around every run / padding boundary, first and last rows, plus
+    seeded random rows; returned as flat b*rows + r indices."""
+    edges = {0, w.rows - 1}
+    start = 0
+    for rows, _ in w.runs:
+        for e in (start, start + rows):
+            edges.update(range(max(0, e - 3), min(w.rows, e + 3)))
+        start += rows
+    for tl in w.text_len:
+        edges.update(range(max(0, tl - 2), min(w.rows, tl + 2)))
+    if w.text_pad:
+        edges.update(range(max(0, w.text_pad - 2), min(w.rows, w.text_pad + 2)))
+    rng = np.random.default_rng(seed)
+    per_item = sorted(edges | set(rng.integers(0, w.rows, count).tolist()))
+    return np.array([b * w.rows + r for b in range(w.batch) for r in per_item], np.uint32)
+
+
+def run_workload_layer(gpu, w, layer=0):
+    q, k, v, wq, wk = workloads.layer_inputs(w, layer)
+    runner = workloads.LayerRunner(gpu, w)
+    qt, kt, vt = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v)
+    wqt, wkt = (gpu.bf16(wq), gpu.bf16(wk)) if w.prologue else (None, None)
+    gpu.begin()
+    out_t = runner.enqueue(qt, kt, vt, wqt, wkt)
+    gpu.submit()
+    out = gpu.read_bf16(out_t, q.size).reshape(q.shape)
+    for t in [qt, kt, vt] + ([wqt, wkt] if w.prologue else []):
+        gpu.free(t)
+    return (q, k, v, wq, wk), out
+
+
+def oracle_layer(w, inputs, rows=None):
+    q, k, v, wq, wk = inputs
+    if w.prologue:
+        cos, sin = w.rope_tables()
+        q, k = prologue_oracle(q, k, wq, wk, cos, sin, w.batch, w.rows, w.heads)
+    tl = np.asarray(w.text_len, np.uint32) if w.text_pad else None
+    ref, _ = O.sdpa(q, k, v, w.limits(), w.batch, w.rows, w.rows, w.heads, w.heads, SCALE, tl,
+                    w.text_pad, rows)
+    return ref
+
+
+@pytest.mark.parametrize("index", [1, 2])
+def test_small_configs_full(gpu, kernel, index):
+    w = workloads.workload(index)
+    inputs, out = run_workload_layer(gpu, w)
+    ref = oracle_layer(w, inputs)
+    gates(out, ref, f"cfg{index}/{kernel}")
+
+
+def test_cfg1_bidirectional_text_reading(gpu):
+    """The benchmark text's other reading of the mask (text sees the whole text
+    run) goes through the same limit table."""
+    import dataclasses
+    w = dataclasses.replace(workloads.workload(1), text_bidirectional=True)
+    assert w.visible_pairs() == 86016
+    inputs, out = run_workload_layer(gpu, w)
+    gates(out, oracle_layer(w, inputs), "cfg1 bidirectional text")
+
+
+@pytest.mark.parametrize("index,count", [(3, 192), (4, 160), (5, 96)])
+def test_large_configs_row_sample(gpu, index, count):
+    w = workloads.workload(index)
+    inputs, out = run_workload_layer(gpu, w)
+    rows = sample_rows(w, count)
+    ref = oracle_layer(w, inputs, rows)
+    flat = out.reshape(w.batch * w.rows, w.heads, 128)
+    gates(flat[rows], ref.reshape(flat.shape)[rows], f"cfg{index} sample of {rows.size} rows")
+    if w.text_pad:  # padding query rows store zeros
+        for b, tl in enumerate(w.text_len):
+            assert not out[b, tl:w.text_pad].any()
+
+
+def test_cfg3_sm100_agrees_with_scalar_kernel_everywhere(gpu):
+    """Whole-output cross-check on the GPU at a size the CPU oracle only samples."""
+    w = workloads.workload(3)
+    _, out_fast = run_workload_layer(gpu, w)
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"scalar")
+    try:
+        _, out_ref = run_workload_layer(gpu, w)
+    finally:
+        gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+    gates(out_fast, bf16_to_f32(out_ref), "cfg3 sm100 vs scalar")
+
+
+# --------------------------------------------------------------------------
+# integer mask indexing, bit-exact on the device
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("case", ["kat", "cfg3", "ragged"])
+def test_mask_indexing_bit_exact(gpu, case):
+    """q = 0 makes every visible key weigh exactly 1, V[s, d] = [s % 128 == d]
+    makes O[r, d] the count of visible keys in residue class d: the output is
+    bf16(count_d * (1 / count)), reproducible exactly from the oracle's dense mask."""
+    if case == "kat":
+        runs, batch, text_len, pad = [(20, 0), (48, 1), (17, 0), (64, 1)], 1, None, 0
+    elif case == "cfg3":
+        runs, batch, text_len, pad = [(256, 0), (1024, 1)], 2, np.array([200, 32], np.uint32), 256
+    else:
+        runs, batch, text_len, pad = [(130, 0), (257, 1), (5, 0), (300, 1)], 2, \
+            np.array([0, 129], np.uint32), 130
+    limits = O.prefix_limits(runs)
+    S, H = int(limits.size), 2
+    q = np.zeros((batch, S, H, 128), np.uint16)
+    k = randn_bf16(np.random.default_rng(1), (batch, S, H, 128))
+    v = np.zeros((batch, S, H, 128), np.uint16)
+    for s in range(S):
+        v[:, s, :, s % 128] = 0x3F80  # 1.0
+    lib = gpu.lib
+    qt, kt, vt, lt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.u32(limits), gpu.new_bf16(q.size)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_attn_block_causal_bf16(
+        gpu.handle, ot, qt, kt, vt, lt, batch, S, H, H, 128,
+        abi._ptr(text_len) if text_len is not None else None, pad, SCALE), "mask probe")
+    gpu.submit()
+    got = gpu.read_bf16(ot, q.size).reshape(q.shape)
+    mask = O.dense_mask(limits, batch, S, S, text_len, pad)
+    onehot = np.zeros((S, 128), np.float32)
+    onehot[np.arange(S), np.arange(S) % 128] = 1
+    counts = mask.astype(np.float32) @ onehot                      # [batch, S, 128]
+    total = mask.sum(-1).astype(np.float32)[..., None]
+    with np.errstate(divide="ignore"):
+        inv = np.where(total > 0, np.float32(1.0) / total, np.float32(0.0)).astype(np.float32)
+    expect = f32_to_bf16((counts * inv).astype(np.float32))
+    for h in range(H):
+        assert np.array_equal(got[:, :, h], expect), f"{case}: mask indexing differs"
+    for t in (qt, kt, vt, lt, ot):
+        gpu.free(t)
+
+
+# --------------------------------------------------------------------------
+# the other entry points and edge cases
+# --------------------------------------------------------------------------
+def test_rect_full_gqa_causal_and_head_major(gpu, kernel):
+    rng = np.random.default_rng(23)
+    lib = gpu.lib
+    # rectangular full attention (image run against the prefix), q_rows != kv_rows
+    QR, KR, H = 200, 333, 4
+    q, k, v = randn_bf16(rng, (QR, H, 128)), randn_bf16(rng, (KR, H, 128)), randn_bf16(rng, (KR, H, 128))
+    qt, kt, vt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.new_bf16(q.size)
+    ref, _ = O.sdpa(q, k, v, None, 1, QR, KR, H, H, SCALE)
+    for fn in (lib.qw_gpu_sdpa_rect_bf16, lib.qw_gpu_flash_sdpa_bf16):
+        gpu.begin()
+        gpu.check(fn(gpu.handle, ot, qt, kt, vt, QR, KR, H, 128, SCALE), "rect")
+        gpu.submit()
+        gates(gpu.read_bf16(ot, q.size), ref, "rect")
+    for t in (qt, kt, vt, ot):
+        gpu.free(t)
+    # causal GQA 8 query heads on 2 kv heads (text tower geometry scaled down)
+    S, QH, KVH = 300, 8, 2
+    q, k, v = randn_bf16(rng, (S, QH, 128)), randn_bf16(rng, (S, KVH, 128)), randn_bf16(rng, (S, KVH, 128))
+    causal = np.arange(1, S + 1, dtype=np.uint32)
+    qt, kt, vt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.new_bf16(q.size)
+    ref, _ = O.sdpa(q, k, v, causal, 1, S, S, QH, KVH, SCALE)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_gqa_causal_bf16(gpu.handle, ot, qt, kt, vt, S, QH, KVH, 128, SCALE), "gqa")
+    gpu.submit()
+    gates(gpu.read_bf16(ot, q.size), ref, "qw causal gqa")
+    # h3 variant: scale folded into Q and re-rounded (h3_shaders.metal:4396-4402)
+    q_scaled = f32_to_bf16(bf16_to_f32(q) * np.float32(SCALE))
+    ref_h3, _ = O.sdpa(q_scaled, k, v, causal, 1, S, S, QH, KVH, 1.0)
+    gpu.begin()
+    gpu.check(lib.h3_gpu_gqa_causal_bf16(gpu.handle, ot, qt, kt, vt, S, QH, KVH, 128, SCALE), "h3 gqa")
+    gpu.submit()
+    gates(gpu.read_bf16(ot, q.size), ref_h3, "h3 causal gqa")
+    for t in (qt, kt, vt, ot):
+        gpu.free(t)
+    # square full attention, token-major and head-major outputs
+    S, H = 257, 3
+    q, k, v = (randn_bf16(rng, (S, H, 128)) for _ in range(3))
+    qt, kt, vt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.new_bf16(q.size)
+    ref, _ = O.sdpa(q, k, v, None, 1, S, S, H, H, SCALE)
+    gpu.begin()
+    gpu.check(lib.h3_gpu_sdpa_bf16(gpu.handle, ot, qt, kt, vt, S, H, 128, SCALE), "sdpa")
+    gpu.submit()
+    gates(gpu.read_bf16(ot, q.size), ref, "square sdpa")
+    gpu.begin()
+    gpu.check(lib.h3_gpu_sdpa_bf16_head_major_output(gpu.handle, ot, qt, kt, vt, S, H, 128, SCALE),
+              "sdpa head-major")
+    gpu.submit()
+    gates(gpu.read_bf16(ot, q.size).reshape(H, S, 128), ref[0].transpose(1, 0, 2), "head-major sdpa")
+    for t in (qt, kt, vt, ot):
+        gpu.free(t)
+
+
+@pytest.mark.parametrize("rows", [1, 63, 128, 129, 257, 640])
+def test_ragged_sizes_and_extreme_limits(gpu, kernel, rows):
+    rng = np.random.default_rng(rows)
+    H = 2
+    q, k, v = (randn_bf16(rng, (rows, H, 128)) for _ in range(3))
+    limits = rng.integers(0, rows + 1, rows).astype(np.uint32)
+    limits[0] = 1
+    limits[-1] = rows
+    if rows > 4:
+        limits[1] = 0                      # a row that sees nothing -> zeros
+        limits[2] = 0xFFFFFFF0             # negative as int32 -> 0
+        limits[3] = rows + 1000            # beyond the key buffer -> capped
+    ref, _ = O.sdpa(q, k, v, limits, 1, rows, rows, H, H, SCALE)
+    out = run_prefix(gpu, q, k, v, limits, rows, rows, H, H)
+    gates(out, ref[0], f"ragged {rows}")
+    if rows > 4:
+        assert not out[1].any() and not out[2].any()
+
+
+def test_key_padding_extremes(gpu, kernel):
+    """text_len = 0 (whole window padded), = text_pad (nothing padded) and a
+    window that is not tile aligned."""
+    rng = np.random.default_rng(99)
+    B, S, H, PAD = 3, 420, 2, 150
+    q, k, v = (randn_bf16(rng, (B, S, H, 128)) for _ in range(3))
+    limits = O.prefix_limits([(PAD, 0), (S - PAD, 1)])
+    text_len = np.array([0, PAD, 77], np.uint32)
+    lib = gpu.lib
+    qt, kt, vt, lt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.u32(limits), gpu.new_bf16(q.size)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_attn_block_causal_bf16(gpu.handle, ot, qt, kt, vt, lt, B, S, H, H, 128,
+                                                abi._ptr(text_len), PAD, SCALE), "padding")
+    gpu.submit()
+    ref, _ = O.sdpa(q, k, v, limits, B, S, S, H, H, SCALE, text_len, PAD)
+    gates(gpu.read_bf16(ot, q.size), ref, "key padding extremes")
+    for t in (qt, kt, vt, lt, ot):
+        gpu.free(t)
+
+
+def test_value_linearity_is_exact(gpu):
+    """attn(q, k, 2v) == 2 * attn(q, k, v) bit for bit (doubling is exact in bf16
+    and in the fp32 accumulator), at a full-size layout."""
+    w = workloads.workload(3)
+    q, k, v, _, _ = workloads.layer_inputs(w, 1)
+    import dataclasses
+    w2 = dataclasses.replace(w, prologue=False)
+    runner = workloads.LayerRunner(gpu, w2)
+    v2 = f32_to_bf16(bf16_to_f32(v) * np.float32(2.0))
+    qt, kt, vt, v2t = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.bf16(v2)
+    o1, o2 = gpu.new_bf16(q.size), gpu.new_bf16(q.size)
+    gpu.begin()
+    runner.enqueue(qt, kt, vt, out=o1)
+    runner.enqueue(qt, kt, v2t, out=o2)
+    gpu.submit()
+    a = bf16_to_f32(gpu.read_bf16(o1, q.size))
+    b = bf16_to_f32(gpu.read_bf16(o2, q.size))
+    assert np.array_equal(a * np.float32(2.0), b)
+    for t in (qt, kt, vt, v2t, o1, o2):
+        gpu.free(t)
+
+
+# --------------------------------------------------------------------------
+# error behaviour mirrors the reference's wrappers
+# --------------------------------------------------------------------------
+def test_error_conventions(gpu):
+    lib = gpu.lib
+    t = gpu.new_bf16(4 * 128)
+    f = gpu.new_f32(4 * 128)
+    lim = gpu.u32(np.ones(1, np.uint32))
+    # op outside a chain (reference h3_gpu.m:274-280)
+    assert lib.qw_gpu_flash_sdpa_bf16(gpu.handle, t, t, t, t, 1, 1, 1, 128, SCALE) == 0
+    assert "h3_gpu_begin() was not called" in gpu.error()
+    gpu.begin()
+    assert lib.h3_gpu_begin(gpu.handle) == 0                  # chain already open
+    assert lib.qw_gpu_flash_sdpa_prefix_bf16(gpu.handle, t, t, t, t, lim, 1, 1, 3, 2, 128, SCALE) == 0
+    assert "unsupported geometry" in gpu.error()              # heads % kv_heads
+    assert lib.qw_gpu_flash_sdpa_prefix_bf16(gpu.handle, t, t, t, t, lim, 1, 1, 1, 1, 64, SCALE) == 0
+    assert "unsupported geometry" in gpu.error()              # head_dim != 128
+    assert lib.qw_gpu_flash_sdpa_prefix_bf16(gpu.handle, t, t, t, t, lim, 8, 1, 1, 1, 128, SCALE) == 0
+    assert "absent or too small" in gpu.error()
+    assert lib.qw_gpu_flash_sdpa_bf16(gpu.handle, t, f, t, t, 1, 1, 1, 128, SCALE) == 0
+    assert "not BF16" in gpu.error()
+    assert lib.qw_gpu_flash_sdpa_prefix_bf16(gpu.handle, t, t, t, t, t, 1, 1, 1, 1, 128, SCALE) == 0
+    assert lib.qw_gpu_flash_sdpa_bf16(gpu.handle, t, t, t, t, 0, 1, 1, 128, SCALE) == 0
+    assert lib.h3_gpu_copy_bf16(gpu.handle, t, 500, t, 0, 100) == 0
+    assert "invalid BF16 blit range" in gpu.error()
+    assert lib.h3_gpu_copy_bf16(gpu.handle, t, 128, t, 0, 128) == 1
+    gpu.submit()
+    assert lib.h3_gpu_submit(gpu.handle) == 0                 # no open chain
+    buf = np.zeros(8, np.uint16)
+    assert lib.h3_gpu_tensor_read_bf16(t, abi._ptr(buf), 10 ** 9) == 0
+    assert lib.h3_gpu_tensor_read_bf16(f, abi._ptr(buf), 4) == 0
+    assert lib.h3_gpu_tensor_write_bf16_range(t, 4 * 128 - 2, abi._ptr(buf), 4) == 0
+    s = gpu.stats()
+    assert s.direct_dispatches >= 1 and s.submissions >= 1 and s.gpu_seconds > 0
+    for x in (t, f, lim):
+        gpu.free(x)
+
+
+def test_rope_tables_on_device_match_host(gpu):
+    lib = gpu.lib
+    cos_t, sin_t = abi.c_tensor(), abi.c_tensor()
+    err = C.create_string_buffer(256)
+    assert lib.qw_pipe_rope_tables(gpu.handle, 23, 8, 8, C.byref(cos_t), C.byref(sin_t), err, 256)
+    cos, sin = abi.rope_tables(23, 8, 8)
+    assert np.array_equal(gpu.read_f32(cos_t, cos.size).reshape(cos.shape), cos)
+    assert np.array_equal(gpu.read_f32(sin_t, sin.size).reshape(sin.shape), sin)
+    lib.h3_gpu_tensor_free(cos_t), lib.h3_gpu_tensor_free(sin_t)
+    assert lib.qw_pipe_rope_tables(gpu.handle, 0, 8, 8, C.byref(cos_t), C.byref(sin_t), err, 256) == 0
+    assert b"bad arguments" in err.value

@@ -1,0 +1,70 @@
+"""CPU: the library's host-side constructors (limits, RoPE tables) against the
+reference fixtures and the oracle.  Integer results are bit-exact."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+from qwen_metal_b200 import abi, workloads
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def rel_l2(a, b):
+    a, b = a.astype(np.float64).ravel(), b.astype(np.float64).ravel()
+    return float(np.sqrt(((a - b) ** 2).sum() / max((b ** 2).sum(), 1e-30)))
+
+
+def test_prefix_limits_bit_exact():
+    layouts = [
+        [(20, 0), (48, 1), (17, 0), (64, 1)],
+        [(64, 0), (256, 1)],
+        [(256, 0), (4096, 1), (4096, 1)],
+        [(1, 0), (1, 1)],
+        [(0, 0), (5, 1), (0, 1), (3, 0)],
+    ]
+    for runs in layouts:
+        assert np.array_equal(abi.prefix_limits(runs), O.prefix_limits(runs))
+
+
+def test_rope_tables_match_reference_fixtures():
+    t = np.load(os.path.join(GOLD, "ref_rope_tables.npz"))
+    for grid in (4, 8):
+        cos, sin = abi.rope_tables(23, grid, grid)
+        assert rel_l2(cos, t[f"pipeline_cos_{grid}"]) <= 1e-6
+        assert rel_l2(sin, t[f"pipeline_sin_{grid}"]) <= 1e-6
+    for case, bh, bw, tb in (("a", [4], [4], [0]), ("b", [3], [4], [8]),
+                             ("c", [6, 8], [8, 8], [20, 17])):
+        cos, sin = abi.rope_tables_blocks(bh, bw, tb)
+        assert rel_l2(cos, t[f"dit_{case}_cos"]) <= 1e-6
+        assert rel_l2(sin, t[f"dit_{case}_sin"]) <= 1e-6
+
+
+def test_rope_tables_equal_oracle_bitwise():
+    for args in ((128, 32, 32), (7, 5, 3)):
+        a, b = abi.rope_tables(*args), O.rope_tables(*args)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    a = abi.rope_tables_blocks([64, 64], [64, 64], [256, 0])
+    b = O.rope_tables_blocks([64, 64], [64, 64], [256, 0])
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+@pytest.mark.parametrize("index,pairs", [(1, 84000), (2, 1187904), (3, 34525332),
+                                         (4, 52461696), (5, 553910784)])
+def test_workload_visible_pairs(index, pairs):
+    """Mask-aware work per config (text rows token-causal, key padding excluded)."""
+    w = workloads.workload(index)
+    assert w.visible_pairs() == pairs
+    tl = np.asarray(w.text_len, np.uint32) if w.text_pad else None
+    assert O.visible_pairs(w.limits(), w.batch, w.rows, w.rows, tl, w.text_pad) == pairs
+
+
+def test_workload_tables_shape():
+    w = workloads.workload(4)
+    cos, sin = w.rope_tables()
+    assert cos.shape == (8448, 64) and sin.shape == (8448, 64)
+    # the second image block sits one max(gh, gw) further along the frame axis
+    assert np.isclose(cos[256, 0], np.cos(256.0), atol=1e-6)
+    assert np.isclose(cos[256 + 4096, 0], np.cos(256.0 + 64.0), atol=1e-6)
