@@ -111,7 +111,10 @@ def test_prologue_legacy_entry_points(gpu):
         got = gpu.read_bf16(t, x.size).reshape(x.shape)
         ref = O.head_rms_norm(x, w, S, H, 1e-6, dbl)
         d = ulp_distance(got, ref)
-        assert d.max() <= 1, d.max()               # warp-tree vs serial sum: rare 1-ulp flips
+        # The warp-tree sum of squares differs from the oracle's serial sum in the
+        # last fp32 bits, which rarely flips a bf16 rounding by one step; with the
+        # double rounding a flipped intermediate moves the product by up to 3 steps.
+        assert d.max() <= (3 if dbl else 1), (dbl, d.max())
         assert (d > 0).mean() < 2e-3, (d > 0).mean()
         gpu.free(t), gpu.free(wt)
     cos, sin = abi.rope_tables(21, 8, 16)
@@ -147,9 +150,19 @@ def test_prologue_fused_matches_three_kernel_sequence(gpu):
                                                w.rows, w.heads, 128, 1e-6), "fused prologue")
     gpu.submit()
     rq, rk = prologue_oracle(q, k, wq, wk, cos, sin, w.batch, w.rows, w.heads)
-    for got, ref in ((gpu.read_bf16(qt, q.size), rq), (gpu.read_bf16(kt, k.size), rk)):
-        d = ulp_distance(got.reshape(ref.shape), ref)
-        assert d.max() <= 1 and (d > 0).mean() < 2e-3, (d.max(), (d > 0).mean())
+    rows = w.batch * w.rows
+    for got, ref, x, wt in ((gpu.read_bf16(qt, q.size), rq, q, wq), (gpu.read_bf16(kt, k.size), rk, k, wk)):
+        got = got.reshape(ref.shape)
+        # Bit-exact except where a normalised value flipped by one bf16 step (see the
+        # legacy test): the rotation carries that step, scaled by |cos| or |sin| <= 1,
+        # into both outputs of the pair.
+        normed = np.abs(bf16_to_f32(O.head_rms_norm(x, wt, rows, w.heads, 1e-6)))
+        pair_max = np.maximum(normed[..., 0::2], normed[..., 1::2])
+        step = np.exp2(np.floor(np.log2(np.maximum(pair_max, 1e-30))) - 7)
+        tol = np.repeat(1.5 * step, 2, axis=-1) + 2.0 ** -9 * np.abs(bf16_to_f32(ref))
+        diff = np.abs(bf16_to_f32(got).astype(np.float64) - bf16_to_f32(ref))
+        assert (diff <= tol).all(), float((diff - tol).max())
+        assert (got != ref).mean() < 2e-3, float((got != ref).mean())
     for t in (qt, kt, wqt, wkt, ct, st):
         gpu.free(t)
 
