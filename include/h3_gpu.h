@@ -147,6 +147,24 @@ int h3_gpu_gqa_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tens
                            uint32_t sequence, uint32_t query_heads, uint32_t kv_heads,
                            uint32_t head_dim, float scale);
 
+/* No counterpart in the reference.  Same arguments, arithmetic and result as
+ * h3_gpu_gqa_causal_bf16, for callers that cannot allocate device memory at the
+ * time of the call: a host that gave the whole GPU to its own arena at start-up
+ * (a later allocation fails there) or a steady-state loop that must not hit the
+ * device-wide synchronisation an allocation or free can imply.  The pre-scaled
+ * query lives in a fixed 8 MiB array inside the library image instead of a
+ * block from the CUDA allocator, so sequence * query_heads * head_dim may not
+ * exceed 4,194,304 (larger calls fail with an error; use the regular op).  The
+ * array is shared by all calls on a GPU: calls that overlap on one GPU race and
+ * must be serialised by the caller.  The first call on a device resolves the
+ * array's address; make it before starting any stream capture.  Requires
+ * head_dim == 128 and a positive finite scale. */
+int h3_gpu_gqa_causal_noalloc_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                   const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                   const h3_gpu_tensor *value, uint32_t sequence,
+                                   uint32_t query_heads, uint32_t kv_heads, uint32_t head_dim,
+                                   float scale);
+
 #ifdef __cplusplus
 }
 #endif
