@@ -184,6 +184,9 @@ def run_product(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     w = workloads.workload(args.workload)
+    if args.layers:
+        import dataclasses
+        w = dataclasses.replace(w, layers=args.layers)
     if w.heads % world:
         sys.exit(f"{w.heads} heads do not shard over {world} ranks")
     heads_local = w.heads // world
@@ -402,6 +405,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", type=int, default=3, choices=[2, 3, 4, 5])
+    ap.add_argument("--layers", type=int, default=0,
+                    help="override the layer count (small captures under a profiler)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", dest="e2e", action="store_false")

@@ -7,11 +7,13 @@
 // one thread per query row, and writes P back to TMEM as bf16 over the S
 // columns so P V reads its A operand straight from TMEM.
 //
-// Warp roles (320 threads):
-//   warps 0-3  softmax + epilogue of sub-tile 0 (TMEM lanes 0..127)
-//   warps 4-7  softmax + epilogue of sub-tile 1
-//   warp  8    MMA issue (one elected lane), TMEM allocation
-//   warp  9    TMA producer (one elected lane)
+// Warp roles (384 threads = 3 warpgroups; registers are moved from the third
+// warpgroup to the two softmax warpgroups with setmaxnreg):
+//   warps 0-3   softmax + epilogue of sub-tile 0 (TMEM lanes 0..127)
+//   warps 4-7   softmax + epilogue of sub-tile 1
+//   warp  8     MMA issue (one elected lane), TMEM allocation
+//   warp  9     TMA producer (one elected lane)
+//   warps 10-11 idle (they only complete the third warpgroup)
 //
 // Mask: every row has an integer key limit (prefix) and the batch item may have
 // a key-padding window.  Key tiles past the largest limit of a sub-tile are
@@ -31,6 +33,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../qw_cuda.h"
 
@@ -42,7 +45,15 @@ constexpr int kTileN = 128;  // keys per tile
 constexpr int kStages = 4;   // K/V ring slots
 constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32 KiB
 constexpr int kHalfTileBytes = kTileBytes / 2;     // one 64-column TMA box
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+// setmaxnreg only redistributes the registers the CTA got at launch
+// (kThreads * 168 = 64512): 2 * 128 * 224 + 128 * 56 = 64512.  Asking for more
+// would block the second softmax warpgroup forever.
+constexpr int kLaunchRegs = 168;
+constexpr int kSoftmaxRegs = 224;
+constexpr int kOtherRegs = 56;
+static_assert(2 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= kThreads * kLaunchRegs,
+              "setmaxnreg budget exceeds the launch allocation");
 constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
@@ -122,7 +133,7 @@ __device__ __forceinline__ bool mbar_try(unsigned long long *bar, uint32_t parit
 
 // Bounded wait.  Returns false when the budget ran out here (recorded) or
 // another thread of the CTA already gave up.
-__device__ __noinline__ bool mbar_wait_slow(SharedControl *ctl, unsigned long long *bar,
+__device__ __forceinline__ bool mbar_wait_slow(SharedControl *ctl, unsigned long long *bar,
                                             uint32_t parity, uint32_t *status, uint32_t where,
                                             uint32_t tile) {
     long long start = clock64();
@@ -242,6 +253,15 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
           "r"((r)[29]), "r"((r)[30]), "r"((r)[31])                                              \
         : "memory")
 
+#define QW_TMEM_ST16(taddr, r)                                                                  \
+    asm volatile(                                                                               \
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                         \
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"             \
+        ::"r"(taddr), "r"((r)[0]), "r"((r)[1]), "r"((r)[2]), "r"((r)[3]), "r"((r)[4]),          \
+          "r"((r)[5]), "r"((r)[6]), "r"((r)[7]), "r"((r)[8]), "r"((r)[9]), "r"((r)[10]),        \
+          "r"((r)[11]), "r"((r)[12]), "r"((r)[13]), "r"((r)[14]), "r"((r)[15])                  \
+        : "memory")
+
 __device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -259,6 +279,53 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+
+// Packed fp32 pairs (one issue slot for two lanes of work on sm_100).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 2^x for a pair on the FMA pipe instead of the special-function unit, which
+// the exponentials of a 128x128 tile otherwise keep as busy as its MMAs keep the
+// tensor pipe: n = round(x) by the 1.5*2^23 trick, r = x - n in [-0.5, 0.5], a
+// cubic for 2^r (exact at r = 0, max relative error 1.2e-4, far below the bf16 rounding of P),
+// then n is added into the exponent field.  x is clamped at -127 (result 0).
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    const float kMagic = 12582912.0f;  // 1.5 * 2^23
+    x.x = fmaxf(x.x, -127.0f);
+    x.y = fmaxf(x.y, -127.0f);
+    const float2 t = fadd2(x, make_float2(kMagic, kMagic));
+    const float2 n = fadd2(t, make_float2(-kMagic, -kMagic));
+    const float2 r = ffma2(n, make_float2(-1.0f, -1.0f), x);
+    float2 q = ffma2(r, make_float2(0.05541782081127167f, 0.05541782081127167f),
+                     make_float2(0.24221134185791016f, 0.24221134185791016f));
+    q = ffma2(q, r, make_float2(0.6931995153427124f, 0.6931995153427124f));
+    q = ffma2(q, r, make_float2(1.0f, 1.0f));
+    float2 out;
+    out.x = __uint_as_float(__float_as_uint(q.x) + (__float_as_uint(t.x) << 23));
+    out.y = __uint_as_float(__float_as_uint(q.y) + (__float_as_uint(t.y) << 23));
+    return out;
 }
 
 __device__ __forceinline__ int row_limit(const KernelParams &p, uint32_t b, uint32_t r) {
@@ -284,6 +351,7 @@ __device__ __forceinline__ bool tile_skipped(const SharedControl *ctl, int j) {
 // ---------------------------------------------------------------------------
 // Softmax + epilogue role: 128 threads per sub-tile, one query row each.
 // ---------------------------------------------------------------------------
+template <int kPoly>
 __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedControl *ctl,
                                              int sub, int tid_in_group, int my_limit, uint32_t b,
                                              uint32_t h, uint32_t row) {
@@ -338,11 +406,11 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         float e0 = -INFINITY, e1 = -INFINITY, e2 = -INFINITY, e3 = -INFINITY;
         if (!neg) {
 #pragma unroll
-            for (int i = 0; i < 128; i += 4) {
-                e0 = fmaxf(e0, __uint_as_float(s[i]));
-                e1 = fmaxf(e1, __uint_as_float(s[i + 1]));
-                e2 = fmaxf(e2, __uint_as_float(s[i + 2]));
-                e3 = fmaxf(e3, __uint_as_float(s[i + 3]));
+            for (int i = 0; i < 128; i += 8) {
+                e0 = fmax3(e0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                e1 = fmax3(e1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                e2 = fmax3(e2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                e3 = fmax3(e3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
             }
         } else {
 #pragma unroll
@@ -385,22 +453,36 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         // P = exp2(sign*score*|c| - m_ref*|c|) as bf16 pairs, written over S.
         const float bias = (m_ref == -INFINITY) ? 0.0f : -m_ref * ac;
         const float cs = sign * ac;
-        uint32_t pk[64];
-        float sum0 = 0.0f, sum1 = 0.0f;
+        // kPoly of every 4 pairs take the polynomial instead of the SFU.  P goes
+        // back to TMEM 32 keys (16 packed columns) at a time.
+        const float2 cs2 = make_float2(cs, cs), bias2 = make_float2(bias, bias);
+        float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int i = 0; i < 128; i += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), cs, bias));
-            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), cs, bias));
-            sum0 += p0;
-            sum1 += p1;
-            pk[i >> 1] = pack_bf16(p0, p1);
+        for (int chunk = 0; chunk < 4; ++chunk) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int e = chunk * 32 + 2 * i;
+                float2 x = ffma2(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])),
+                                 cs2, bias2);
+                float2 pr;
+                if ((i & 3) < kPoly) {
+                    pr = exp2_poly2(x);
+                } else {
+                    pr.x = fast_exp2(x.x);
+                    pr.y = fast_exp2(x.y);
+                }
+                if (i & 1) sum_b = fadd2(sum_b, pr);
+                else sum_a = fadd2(sum_a, pr);
+                pk[i] = pack_bf16(pr.x, pr.y);
+            }
+            QW_TMEM_ST16(tmem_s + chunk * 16, pk);
         }
-        QW_TMEM_ST32(tmem_s + 0, pk + 0);
-        QW_TMEM_ST32(tmem_s + 32, pk + 32);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p);
-        l_run += sum0 + sum1;
+        sum_a = fadd2(sum_a, sum_b);
+        l_run += sum_a.x + sum_a.y;
         ++processed;
     }
 
@@ -601,6 +683,7 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
     }
 }
 
+template <int kPoly>
 __global__ void __launch_bounds__(kThreads, 1)
 qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
                      const __grid_constant__ CUtensorMap map_k,
@@ -690,10 +773,15 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncthreads();
 
     if (tid < kSoftmaxThreads) {
-        softmax_role(p, ctl, sub, tid_in_group, my_limit, b, h, my_row);
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+        softmax_role<kPoly>(p, ctl, sub, tid_in_group, my_limit, b, h, my_row);
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+    }
+    if (tid < kSoftmaxThreads) {
     } else if (warp == kMmaWarp) {
         if (lane == 0) mma_role(p, ctl, smem_q, smem_kv);
-    } else if (lane == 0) {
+    } else if (warp == kTmaWarp && lane == 0) {
         tma_role(p, ctl, smem_kv, &map_k, &map_v, b, kvh);
         // Q loads of active sub-tiles must have landed as well.
         for (int i = 0; i < 2; ++i) {
@@ -747,6 +835,32 @@ int make_map(CUtensorMap *map, const void *base, uint32_t batch, uint32_t rows, 
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+typedef void (*AttnKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                           const KernelParams);
+
+// How many of every 4 score pairs take the polynomial exp2 (QW_CUDA_EXP_POLY=0..4
+// overrides the default for tuning).
+AttnKernel pick_kernel() {
+    static AttnKernel chosen = nullptr;
+    if (!chosen) {
+        int poly = 2;
+        const char *env = getenv("QW_CUDA_EXP_POLY");
+        if (env && env[0] >= '0' && env[0] <= '4' && !env[1]) poly = env[0] - '0';
+        switch (poly) {
+            case 0: chosen = qw_attn_sm100_kernel<0>; break;
+            case 1: chosen = qw_attn_sm100_kernel<1>; break;
+            case 3: chosen = qw_attn_sm100_kernel<3>; break;
+            case 4: chosen = qw_attn_sm100_kernel<4>; break;
+            default: chosen = qw_attn_sm100_kernel<2>; break;
+        }
+        if (cudaFuncSetAttribute(chosen, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemBytes) != cudaSuccess) {
+            chosen = nullptr;
+        }
+    }
+    return chosen;
+}
+
 }  // namespace
 
 extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream stream_) {
@@ -756,14 +870,8 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     // TMA needs 16-byte aligned bases; cudaMalloc gives 256.
     if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15u)
         return (int)cudaErrorMisalignedAddress;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(qw_attn_sm100_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        attr_set = true;
-    }
+    AttnKernel kernel = pick_kernel();
+    if (!kernel) return (int)cudaGetLastError();
     CUtensorMap map_q, map_k, map_v;
     int rc;
     if ((rc = make_map(&map_q, a->q, a->batch, a->q_rows, a->heads))) return rc;
@@ -786,6 +894,6 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.head_major_out = a->head_major_out;
     dim3 grid((a->q_rows + 2 * kTileM - 1) / (2 * kTileM), a->heads, a->batch);
-    qw_attn_sm100_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
     return (int)cudaGetLastError();
 }
