@@ -33,6 +33,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "../qw_cuda.h"
@@ -47,11 +48,11 @@ constexpr int kTileBytes = kTileN * kHeadDim * 2;  // 32 KiB
 constexpr int kHalfTileBytes = kTileBytes / 2;     // one 64-column TMA box
 constexpr int kThreads = 384;
 // setmaxnreg only redistributes the registers the CTA got at launch
-// (kThreads * 168 = 64512): 2 * 128 * 224 + 128 * 56 = 64512.  Asking for more
+// (kThreads * 168 = 64512): 2 * 128 * 208 + 128 * 88 = 64512.  Asking for more
 // would block the second softmax warpgroup forever.
 constexpr int kLaunchRegs = 168;
-constexpr int kSoftmaxRegs = 224;
-constexpr int kOtherRegs = 56;
+constexpr int kSoftmaxRegs = 208;
+constexpr int kOtherRegs = 88;
 static_assert(2 * 128 * kSoftmaxRegs + 128 * kOtherRegs <= kThreads * kLaunchRegs,
               "setmaxnreg budget exceeds the launch allocation");
 constexpr int kSoftmaxThreads = 256;
@@ -72,7 +73,8 @@ enum Barrier : int {
     kBarSFull = kBarKvEmpty + kStages,    // 2: S_i complete in TMEM
     kBarPFull = kBarSFull + 2,            // 2: P_i written (128 arrivals)
     kBarOFinal = kBarPFull + 2,           // 2: last P V of sub-tile i complete
-    kBarCount = kBarOFinal + 2
+    kBarDebug = kBarOFinal + 2,           // trace builds: group completion probe
+    kBarCount = kBarDebug + 1
 };
 
 struct __align__(16) SharedControl {
@@ -91,6 +93,9 @@ struct KernelParams {
     __nv_bfloat16 *out;
     const int32_t *kv_limit;
     uint32_t *status;
+#ifdef QW_ATTN_TRACE
+    unsigned long long *trace;  // event log of block (0,0,0), dumped to $QW_CUDA_ATTN_TRACE
+#endif
     int per_batch_limits;
     int causal;
     uint32_t causal_offset;
@@ -206,23 +211,28 @@ constexpr uint32_t make_idesc(bool b_mn_major) {
 constexpr uint32_t kIdescQK = make_idesc(false);
 constexpr uint32_t kIdescPV = make_idesc(true);
 
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
+// Descriptors travel as (low word, high word): stepping through a tile only
+// changes the start-address field in the low word, so each MMA costs one
+// integer add per operand on the issuing thread.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                       uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
                                        uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -328,6 +338,27 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     return out;
 }
 
+// Pipeline event log, compiled in only with -DQW_ATTN_TRACE (a debugging build).
+#ifdef QW_ATTN_TRACE
+// Event log for pipeline analysis: (role, event, tile) and the SM clock, written
+// by one thread per role of block (0, 0, 0) when a trace buffer is attached.
+constexpr int kTraceSlots = 4096;
+__device__ __forceinline__ void trace_event(const KernelParams &p, int role, int event, int tile,
+                                            uint32_t &cursor) {
+    // One private region per role and a register cursor: a plain store, no
+    // round trip, so the log barely perturbs what it measures.
+    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && cursor < 1000) {
+        p.trace[1 + role * 1024 + cursor] =
+            ((unsigned long long)(role << 20 | event << 12 | (tile & 0xfff)) << 40) |
+            ((unsigned long long)clock64() & 0xffffffffffull);
+        ++cursor;
+    }
+}
+#define QW_TRACE(role, event, tile) trace_event(p, role, event, tile, trace_cursor)
+#else
+#define QW_TRACE(role, event, tile) ((void)0)
+#endif
+
 __device__ __forceinline__ int row_limit(const KernelParams &p, uint32_t b, uint32_t r) {
     if (r >= p.q_rows) return 0;
     if (p.text_pad && r >= p.text_len[b] && r < p.text_pad) return 0;  // padding query row
@@ -368,6 +399,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     const float c = p.scale_log2;
     const bool neg = c < 0.0f;
 
+    [[maybe_unused]] uint32_t trace_cursor = 0;
     float m_run = -INFINITY;  // running extreme of the raw scores (max, or min when c < 0)
     float m_ref = -INFINITY;  // extreme the stored exponents refer to
     float l_run = 0.0f;
@@ -382,6 +414,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         if (!ok) break;
         phase ^= 1u;
         tc_fence_after();
+        if (tid_in_group == 0) QW_TRACE(sub, 0, j);
 
         uint32_t s[128];
         QW_TMEM_LD32(tmem_s + 0, s + 0);
@@ -389,6 +422,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         QW_TMEM_LD32(tmem_s + 64, s + 64);
         QW_TMEM_LD32(tmem_s + 96, s + 96);
         tmem_wait_ld();
+        if (tid_in_group == 0) QW_TRACE(sub, 1, j);
 
         const int key0 = j * kTileN;
         const bool pad_hit = pad_hi > pad_lo && key0 < pad_hi && key0 + kTileN > pad_lo;
@@ -449,6 +483,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
             tmem_wait_st();
         }
         l_run *= alpha;
+        if (tid_in_group == 0) QW_TRACE(sub, 2, j);
 
         // P = exp2(sign*score*|c| - m_ref*|c|) as bf16 pairs, written over S.
         const float bias = (m_ref == -INFINITY) ? 0.0f : -m_ref * ac;
@@ -478,9 +513,11 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
             }
             QW_TMEM_ST16(tmem_s + chunk * 16, pk);
         }
+        if (tid_in_group == 0) QW_TRACE(sub, 3, j);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p);
+        if (tid_in_group == 0) QW_TRACE(sub, 4, j);
         sum_a = fadd2(sum_a, sum_b);
         l_run += sum_a.x + sum_a.y;
         ++processed;
@@ -529,27 +566,34 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
 // ---------------------------------------------------------------------------
 // MMA issue role (one thread).
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_addr, uint32_t k_addr) {
+// High words of the two descriptor kinds (everything but the start address).
+constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // SBO, version 1, SWIZZLE_128B
+}
+constexpr uint32_t desc_lo_fixed(uint32_t lbo_bytes) { return ((lbo_bytes >> 4) & 0x3FFFu) << 16; }
+constexpr uint32_t kDescHi = desc_hi(1024);
+constexpr uint32_t kDescLoKMajor = desc_lo_fixed(16);               // LBO unused for K-major SW128
+constexpr uint32_t kDescLoVMajor = desc_lo_fixed(kHalfTileBytes);   // next 64-column half
+
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_t k_lo) {
     // K-major operands, 128B swizzle: 8-row groups 1024 B apart; the second
     // 64-column box sits one half tile further; 16 columns = 32 B per step.
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-        uint32_t off = (uint32_t)(kk >> 2) * kHalfTileBytes + (uint32_t)(kk & 3) * 32u;
-        mma_ss(d_tmem, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024),
-               kIdescQK, kk > 0 ? 1u : 0u);
+        const uint32_t off = ((uint32_t)(kk >> 2) * kHalfTileBytes + (uint32_t)(kk & 3) * 32u) >> 4;
+        mma_ss(d_tmem, q_lo + off, kDescHi, k_lo + off, kDescHi, kIdescQK, kk > 0 ? 1u : 0u);
     }
 }
 
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_addr,
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo,
                                          bool accumulate) {
     // A = P from TMEM (16 keys = 8 packed columns per step).  B = V, MN-major:
     // 16 keys = 2 groups of 8 rows (1024 B apart), the two 64-wide column
     // halves one half tile apart.
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-        mma_ts(d_tmem, p_tmem + (uint32_t)kk * 8u,
-               smem_desc(v_addr + (uint32_t)kk * 2048u, kHalfTileBytes, 1024), kIdescPV,
-               (accumulate || kk > 0) ? 1u : 0u);
+        mma_ts(d_tmem, p_tmem + (uint32_t)kk * 8u, v_lo + (uint32_t)(kk * 2048 >> 4), kDescHi,
+               kIdescPV, (accumulate || kk > 0) ? 1u : 0u);
     }
 }
 
@@ -559,22 +603,28 @@ __device__ __forceinline__ int next_tile(const SharedControl *ctl, int j, int n_
     return j < n_max ? j : n_max;
 }
 
-__device__ void mma_role(const KernelParams &p, SharedControl *ctl, uint8_t *smem_q,
-                         uint8_t *smem_kv) {
+__device__ __forceinline__ void mma_role(const KernelParams &p, SharedControl *ctl,
+                                         uint8_t *smem_q, uint8_t *smem_kv) {
     const int n0 = ctl->n_tiles[0], n1 = ctl->n_tiles[1];
     const int n_max = max(n0, n1);
     int j = next_tile(ctl, -1, n_max);
     if (j >= n_max) return;
     const uint32_t tmem = ctl->tmem_base;
-    const uint32_t q_addr[2] = {smem_u32(smem_q), smem_u32(smem_q + kTileBytes)};
+    // Low descriptor words: start address in 16-byte units plus the fixed LBO field.
+    const uint32_t q_lo[2] = {(smem_u32(smem_q) >> 4) | kDescLoKMajor,
+                              (smem_u32(smem_q + kTileBytes) >> 4) | kDescLoKMajor};
+    const uint32_t kv_lo = smem_u32(smem_kv) >> 4;  // slot s starts (s * kTileBytes) >> 4 further
     const uint32_t s_tmem[2] = {tmem + kTmemS0, tmem + kTmemS1};
     const uint32_t o_tmem[2] = {tmem + kTmemO0, tmem + kTmemO1};
     const int n_sub[2] = {n0, n1};
     uint32_t p_phase[2] = {0, 0};
     bool o_started[2] = {false, false};
     uint32_t t = 0;  // ring position (K and V tiles alternate)
+    [[maybe_unused]] uint32_t trace_cursor = 0;
+    [[maybe_unused]] uint32_t dbg_phase = 0;
     const uint32_t where = 2u << 16;
 
+#pragma unroll
     for (int i = 0; i < 2; ++i)
         if (n_sub[i] > 0 &&
             !mbar_wait(ctl, &ctl->bars[kBarQFull + i], 0, p.status, where | (kBarQFull + i), 0))
@@ -586,10 +636,11 @@ __device__ void mma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
                        where | (kBarKvFull + slot), (uint32_t)j))
             return;
         tc_fence_after();
-        uint32_t k_addr = smem_u32(smem_kv + (size_t)slot * kTileBytes);
+        const uint32_t k_lo = (kv_lo + slot * (kTileBytes >> 4)) | kDescLoKMajor;
+#pragma unroll
         for (int i = 0; i < 2; ++i)
             if (j < n_sub[i]) {
-                issue_qk(s_tmem[i], q_addr[i], k_addr);
+                issue_qk(s_tmem[i], q_lo[i], k_lo);
                 tc_commit(&ctl->bars[kBarSFull + i]);
             }
         tc_commit(&ctl->bars[kBarKvEmpty + slot]);
@@ -604,12 +655,15 @@ __device__ void mma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
             k_par = (t / kStages) & 1u;
             ++t;
         }
+        QW_TRACE(2, 6, j);
         if (!mbar_wait(ctl, &ctl->bars[kBarKvFull + v_slot], v_par, p.status,
                        where | (kBarKvFull + v_slot), (uint32_t)j))
             return;
-        const uint32_t v_addr = smem_u32(smem_kv + (size_t)v_slot * kTileBytes);
-        const uint32_t k_addr = smem_u32(smem_kv + (size_t)k_slot * kTileBytes);
+        QW_TRACE(2, 7, j);
+        const uint32_t v_lo = (kv_lo + v_slot * (kTileBytes >> 4)) | kDescLoVMajor;
+        const uint32_t k_lo = (kv_lo + k_slot * (kTileBytes >> 4)) | kDescLoKMajor;
         bool k_ready = false;
+#pragma unroll
         for (int i = 0; i < 2; ++i) {
             if (j < n_sub[i]) {
                 if (!mbar_wait(ctl, &ctl->bars[kBarPFull + i], p_phase[i], p.status,
@@ -617,20 +671,33 @@ __device__ void mma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
                     return;
                 p_phase[i] ^= 1u;
                 tc_fence_after();
-                issue_pv(o_tmem[i], s_tmem[i], v_addr, o_started[i]);
+                QW_TRACE(2, i, j);
+                issue_pv(o_tmem[i], s_tmem[i], v_lo, o_started[i]);
                 o_started[i] = true;
+                QW_TRACE(2, 4 + i, j);
             }
             if (i == 1) tc_commit(&ctl->bars[kBarKvEmpty + v_slot]);
             if (jn < n_max && jn < n_sub[i]) {
                 if (!k_ready) {
+                    QW_TRACE(2, 8, jn);
                     if (!mbar_wait(ctl, &ctl->bars[kBarKvFull + k_slot], k_par, p.status,
                                    where | (kBarKvFull + k_slot), (uint32_t)jn))
                         return;
                     tc_fence_after();
                     k_ready = true;
+                    QW_TRACE(2, 9, jn);
                 }
-                issue_qk(s_tmem[i], q_addr[i], k_addr);
+                issue_qk(s_tmem[i], q_lo[i], k_lo);
                 tc_commit(&ctl->bars[kBarSFull + i]);
+                QW_TRACE(2, 2 + i, jn);
+#ifdef QW_ATTN_TRACE_SERIAL
+                // Probe: wait until the group just issued has executed.
+                tc_commit(&ctl->bars[kBarDebug]);
+                if (!mbar_wait(ctl, &ctl->bars[kBarDebug], dbg_phase, p.status, where | kBarDebug, 0))
+                    return;
+                dbg_phase ^= 1u;
+                QW_TRACE(2, 10 + i, jn);
+#endif
             }
         }
         if (jn < n_max) {
@@ -715,6 +782,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_init(&ctl->bars[kBarPFull + i], kTileM);
             mbar_init(&ctl->bars[kBarOFinal + i], 1);
         }
+        mbar_init(&ctl->bars[kBarDebug], 1);
         ctl->abort_flag = 0;
         int lo = 0, hi = 0;
         if (p.text_pad && p.text_len[b] < p.text_pad) {
@@ -835,6 +903,44 @@ int make_map(CUtensorMap *map, const void *base, uint32_t batch, uint32_t rows, 
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+#ifdef QW_ATTN_TRACE
+// QW_CUDA_ATTN_TRACE=<file>: attach an event log to every launch and dump it after
+// each one (synchronous; a debugging aid, never set in production runs).
+unsigned long long *trace_buffer() {
+    static unsigned long long *buffer = nullptr;
+    static bool looked = false;
+    if (!looked) {
+        looked = true;
+        const char *path = getenv("QW_CUDA_ATTN_TRACE");
+        if (path && *path) {
+            if (cudaMalloc(&buffer, kTraceSlots * 8) != cudaSuccess) buffer = nullptr;
+            else cudaMemset(buffer, 0, kTraceSlots * 8);
+        }
+    }
+    return buffer;
+}
+
+void trace_dump(cudaStream_t stream) {
+    unsigned long long *buffer = trace_buffer();
+    if (!buffer) return;
+    static unsigned long long host[kTraceSlots];
+    cudaStreamSynchronize(stream);
+    cudaMemcpy(host, buffer, sizeof(host), cudaMemcpyDeviceToHost);
+    cudaMemset(buffer, 0, kTraceSlots * 8);
+    FILE *f = fopen(getenv("QW_CUDA_ATTN_TRACE"), "a");
+    if (!f) return;
+    fprintf(f, "launch\n");
+    for (int i = 1; i < kTraceSlots; ++i) {
+        unsigned long long w = host[i];
+        if (!w) continue;
+        unsigned tag = (unsigned)(w >> 40);
+        fprintf(f, "%u %u %u %llu\n", tag >> 20, (tag >> 12) & 0xff, tag & 0xfff,
+                w & 0xffffffffffull);
+    }
+    fclose(f);
+}
+#endif
+
 typedef void (*AttnKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
                            const KernelParams);
 
@@ -843,7 +949,7 @@ typedef void (*AttnKernel)(const CUtensorMap, const CUtensorMap, const CUtensorM
 AttnKernel pick_kernel() {
     static AttnKernel chosen = nullptr;
     if (!chosen) {
-        int poly = 2;
+        int poly = 0;
         const char *env = getenv("QW_CUDA_EXP_POLY");
         if (env && env[0] >= '0' && env[0] <= '4' && !env[1]) poly = env[0] - '0';
         switch (poly) {
@@ -881,6 +987,9 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     p.out = static_cast<__nv_bfloat16 *>(a->out);
     p.kv_limit = a->kv_limit;
     p.status = a->status;
+#ifdef QW_ATTN_TRACE
+    p.trace = trace_buffer();
+#endif
     p.per_batch_limits = a->per_batch_limits;
     p.causal = a->causal;
     p.causal_offset = a->causal_offset;
@@ -895,5 +1004,9 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     p.head_major_out = a->head_major_out;
     dim3 grid((a->q_rows + 2 * kTileM - 1) / (2 * kTileM), a->heads, a->batch);
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
-    return (int)cudaGetLastError();
+    rc = (int)cudaGetLastError();
+#ifdef QW_ATTN_TRACE
+    if (p.trace && !rc) trace_dump(stream);
+#endif
+    return rc;
 }
