@@ -71,7 +71,7 @@ enum Barrier : int {
     kBarKvFull = 2,                       // kStages
     kBarKvEmpty = kBarKvFull + kStages,   // kStages
     kBarSFull = kBarKvEmpty + kStages,    // 2: S_i complete in TMEM
-    kBarPFull = kBarSFull + 2,            // 2: P_i written (128 arrivals)
+    kBarPFull = kBarSFull + 2,            // 2: P_i written (one arrival per warp)
     kBarOFinal = kBarPFull + 2,           // 2: last P V of sub-tile i complete
     kBarDebug = kBarOFinal + 2,           // trace builds: group completion probe
     kBarCount = kBarDebug + 1
@@ -514,9 +514,9 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
             QW_TMEM_ST16(tmem_s + chunk * 16, pk);
         }
         if (tid_in_group == 0) QW_TRACE(sub, 3, j);
-        tmem_wait_st();
+        tmem_wait_st();  // warp-collective: every lane's stores have landed
         tc_fence_before();
-        mbar_arrive(bar_p);
+        if ((tid_in_group & 31) == 0) mbar_arrive(bar_p);  // one arrival per warp
         if (tid_in_group == 0) QW_TRACE(sub, 4, j);
         sum_a = fadd2(sum_a, sum_b);
         l_run += sum_a.x + sum_a.y;
@@ -779,7 +779,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctl->bars[kBarSFull + i], 1);
-            mbar_init(&ctl->bars[kBarPFull + i], kTileM);
+            mbar_init(&ctl->bars[kBarPFull + i], kTileM / 32);
             mbar_init(&ctl->bars[kBarOFinal + i], 1);
         }
         mbar_init(&ctl->bars[kBarDebug], 1);

@@ -14,6 +14,7 @@ It writes only small data files next to this script:
                            layout from tests/dit_fixture/meta.json
   host_ref_rope.json       the 144 released-table samples of tests/host_ref.h:19-57
   dit_segments.json        run layout of fixture case c (tests/dit_fixture/meta.json)
+  reference_abi_names.json the function names declared by h3_gpu.h and qwen_gpu_ext.h
   kat_prefix_sdpa.json     verdict of the reference's tests/test_prefix_kernel.c
                            compiled unmodified with the CPU oracle behind the op
                            (oracle/_ref/test_prefix_kernel_oracle), plus a checksum of
@@ -77,6 +78,15 @@ def main():
                "heads": meta["heads"], "head_dim": meta["head_dim"], "eps": meta["eps"],
                "cases": meta["cases"]},
               open(os.path.join(HERE, "dit_segments.json"), "w"))
+
+    # every function name the two ABI headers declare (names only)
+    abi_names = set()
+    for header in ("h3_gpu.h", "qwen_gpu_ext.h"):
+        text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ref, header)).read(), flags=re.S)
+        abi_names |= set(re.findall(r"\b((?:h3_gpu|qw_gpu)_\w+)\s*\(", text))
+    json.dump({"source": "h3_gpu.h, qwen_gpu_ext.h (declared function names)",
+               "names": sorted(abi_names)},
+              open(os.path.join(HERE, "reference_abi_names.json"), "w"))
 
     subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "all", "ref", f"REF={ref}"],
                           stdout=subprocess.DEVNULL)
