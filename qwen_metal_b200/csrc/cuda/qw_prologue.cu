@@ -1,16 +1,22 @@
 // Fused per-head QK RMSNorm + interleaved 3-axis RoPE (HBM-bound prologue).
 //
 // A head is 128 bf16 = 256 B = sixteen 16-byte vectors, so a half-warp owns one
-// (row, head) of one tensor: one 16-byte load per lane (8 elements = 4 whole
-// RoPE pairs), a 4-step shuffle reduction for the sum of squares, then the
-// rotation from two 16-byte f32 table loads, one 16-byte store.  Q and K each
-// cross HBM exactly once in each direction.
+// head at a time: one 16-byte load per lane (8 elements = 4 whole RoPE pairs), a
+// 4-step shuffle reduction for the sum of squares, then the rotation, one
+// 16-byte store.  Each half-warp walks all heads of one (row, tensor) strip with
+// its slice of the norm weight and of the row's cos/sin held in registers, four
+// heads in flight at a time.  Q and K each cross HBM exactly once in each
+// direction.  The kernel was instruction-bound before it was HBM-bound, so the
+// bf16 roundings use cvt.rn.bf16x2.f32 and the inverse norm uses rsqrtf.
 //
 // Arithmetic follows the reference's three separate kernels including the bf16
 // store between norm and rotation: n = bf16(x * inv * w) (h3_shaders.metal:
 // 4309-4329; bf16(bf16(x*inv)*w) for the double-rounding variant :4975-4997),
 // then (e, o) <- bf16(e*c - o*s), bf16(e*s + o*c) (h3_shaders.metal:4864-4890),
-// products and sums as separate fp32 operations.
+// products and sums as separate fp32 operations.  The sum of squares is reduced
+// as a tree and 1/sqrt is within 2 ulp, where the reference shader runs a serial
+// fma chain and its own rsqrt: a normalised value differs from a serial CPU
+// restatement by one bf16 step in about 1 element in 10^5.
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -46,69 +52,99 @@ struct Params {
     uint32_t rows, table_rows, heads;
     float eps;
     int double_round;
-    unsigned long long units;  // rows * heads * tensors
+    uint32_t strips;  // rows * tensors: one half-warp walks the heads of one (row, tensor)
     int tensors;
 };
 
+// Two floats -> packed bf16 pair, round to nearest even in one instruction
+// (the same rounding as the integer trick for every finite value).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Heads a half-warp has in flight at once (independent 16-byte loads; the
+// kernel is HBM-bound once the instruction count is small enough).
+constexpr int kHeadsPerTrip = 4;
+
+// A half-warp owns one (row, tensor) strip: it keeps its 8-element slice of the
+// norm weight and of the row's cos/sin in registers and walks the heads, four at
+// a time.  Lane l holds elements [8l, 8l+8) of every head = RoPE pairs 4l..4l+3.
 __global__ void __launch_bounds__(256) qw_prologue_kernel(const Params p) {
     const int lane16 = threadIdx.x & 15;
-    unsigned long long unit = ((unsigned long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
-    const unsigned long long stride = ((unsigned long long)gridDim.x * blockDim.x) >> 4;
-    // All 16 lanes of a half-warp share `unit`; both halves of a warp stay in
-    // the loop together because units is padded to an even count by the host.
-    for (; unit < p.units; unit += stride) {
-        // Unit order: (row, tensor, head) so q and k of a row share table lines.
-        const unsigned long long per_row = (unsigned long long)p.heads * p.tensors;
-        const uint32_t row = (uint32_t)(unit / per_row);
-        const uint32_t rem = (uint32_t)(unit % per_row);
-        const int is_k = rem >= p.heads;
-        const uint32_t head = is_k ? rem - p.heads : rem;
+    const uint32_t half_warps = (gridDim.x * blockDim.x) >> 4;
+    // Both half-warps of a warp run the same number of trips (the strip count is
+    // padded to an even number by the host): the shuffles need the whole warp.
+    for (uint32_t strip = (blockIdx.x * blockDim.x + threadIdx.x) >> 4; strip < p.strips;
+         strip += half_warps) {
+        const uint32_t row = strip / (uint32_t)p.tensors;
+        const bool is_k = (strip % (uint32_t)p.tensors) != 0;
         const bool live = row < p.rows;
-        const size_t vec = ((size_t)row * p.heads + head) * 16 + lane16;
-        const uint4 *src = is_k ? p.k_in : p.q_in;
-        uint4 *dst = is_k ? p.k_out : p.q_out;
+        const uint4 *src = (is_k ? p.k_in : p.q_in) + (size_t)row * p.heads * 16 + lane16;
+        uint4 *dst = (is_k ? p.k_out : p.q_out) + (size_t)row * p.heads * 16 + lane16;
         const uint4 *w = is_k ? p.wk : p.wq;
-
-        uint4 x = live ? src[vec] : make_uint4(0, 0, 0, 0);
-        float v[8] = {bf16_lo(x.x), bf16_hi(x.x), bf16_lo(x.y), bf16_hi(x.y),
-                      bf16_lo(x.z), bf16_hi(x.z), bf16_lo(x.w), bf16_hi(x.w)};
+        float wf[8], cc[4], sn[4];
         if (w) {
-            float ss = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
-#pragma unroll
-            for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off, 16);
-            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), p.eps)));
-            uint4 wv = w[lane16];
-            float wf[8] = {bf16_lo(wv.x), bf16_hi(wv.x), bf16_lo(wv.y), bf16_hi(wv.y),
-                           bf16_lo(wv.z), bf16_hi(wv.z), bf16_lo(wv.w), bf16_hi(wv.w)};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                float n = __fmul_rn(v[i], inv);
-                if (p.double_round) n = round_bf16(n);
-                v[i] = round_bf16(__fmul_rn(n, wf[i]));
-            }
+            const uint4 wv = w[lane16];
+            wf[0] = bf16_lo(wv.x); wf[1] = bf16_hi(wv.x); wf[2] = bf16_lo(wv.y); wf[3] = bf16_hi(wv.y);
+            wf[4] = bf16_lo(wv.z); wf[5] = bf16_hi(wv.z); wf[6] = bf16_lo(wv.w); wf[7] = bf16_hi(wv.w);
         }
         if (p.cos_t) {
-            const size_t t = (size_t)(row % p.table_rows) * 16 + lane16;
-            float4 c = live ? p.cos_t[t] : make_float4(1, 1, 1, 1);
-            float4 s = live ? p.sin_t[t] : make_float4(0, 0, 0, 0);
-            const float cc[4] = {c.x, c.y, c.z, c.w};
-            const float sn[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float e = v[2 * i], o = v[2 * i + 1];
-                v[2 * i] = __fsub_rn(__fmul_rn(e, cc[i]), __fmul_rn(o, sn[i]));
-                v[2 * i + 1] = __fadd_rn(__fmul_rn(e, sn[i]), __fmul_rn(o, cc[i]));
-            }
+            const size_t t = (size_t)((live ? row : 0u) % p.table_rows) * 16 + lane16;
+            const float4 c = p.cos_t[t], s4 = p.sin_t[t];
+            cc[0] = c.x; cc[1] = c.y; cc[2] = c.z; cc[3] = c.w;
+            sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
         }
-        if (live) {
-            uint4 y;
-            y.x = f32_to_bf16_bits(v[0]) | (f32_to_bf16_bits(v[1]) << 16);
-            y.y = f32_to_bf16_bits(v[2]) | (f32_to_bf16_bits(v[3]) << 16);
-            y.z = f32_to_bf16_bits(v[4]) | (f32_to_bf16_bits(v[5]) << 16);
-            y.w = f32_to_bf16_bits(v[6]) | (f32_to_bf16_bits(v[7]) << 16);
-            dst[vec] = y;
+        for (uint32_t head0 = 0; head0 < p.heads; head0 += kHeadsPerTrip) {
+            uint4 x[kHeadsPerTrip];
+#pragma unroll
+            for (int u = 0; u < kHeadsPerTrip; ++u)
+                x[u] = (live && head0 + u < p.heads) ? src[(size_t)(head0 + u) * 16]
+                                                     : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < kHeadsPerTrip; ++u) {
+                float v[8] = {bf16_lo(x[u].x), bf16_hi(x[u].x), bf16_lo(x[u].y), bf16_hi(x[u].y),
+                              bf16_lo(x[u].z), bf16_hi(x[u].z), bf16_lo(x[u].w), bf16_hi(x[u].w)};
+                uint32_t y[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+                if (w) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+                    for (int off = 8; off > 0; off >>= 1)
+                        ss += __shfl_xor_sync(0xffffffffu, ss, off, 16);
+                    // mean = ss / 128 exactly; 1/sqrt to within 2 ulp of the reference's rsqrt
+                    const float inv = rsqrtf(__fadd_rn(ss * 0.0078125f, p.eps));
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        float n0 = __fmul_rn(v[i], inv), n1 = __fmul_rn(v[i + 1], inv);
+                        if (p.double_round) {
+                            const uint32_t r = pack_bf16x2(n0, n1);
+                            n0 = bf16_lo(r);
+                            n1 = bf16_hi(r);
+                        }
+                        y[i >> 1] = pack_bf16x2(__fmul_rn(n0, wf[i]), __fmul_rn(n1, wf[i + 1]));
+                    }
+                    if (p.cos_t) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {  // the bf16 store between norm and rotation
+                            v[2 * i] = bf16_lo(y[i]);
+                            v[2 * i + 1] = bf16_hi(y[i]);
+                        }
+                    }
+                }
+                if (p.cos_t) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float e = v[2 * i], o = v[2 * i + 1];
+                        y[i] = pack_bf16x2(__fsub_rn(__fmul_rn(e, cc[i]), __fmul_rn(o, sn[i])),
+                                           __fadd_rn(__fmul_rn(e, sn[i]), __fmul_rn(o, cc[i])));
+                    }
+                }
+                if (live && head0 + u < p.heads)
+                    dst[(size_t)(head0 + u) * 16] = make_uint4(y[0], y[1], y[2], y[3]);
+            }
         }
     }
 }
@@ -154,12 +190,14 @@ extern "C" int qwcu_prologue_launch(const qwcu_prologue_args *a, qwcu_stream str
     p.eps = a->epsilon;
     p.double_round = a->double_round;
     p.tensors = a->k_in ? 2 : 1;
-    unsigned long long units = (unsigned long long)a->rows * a->heads * p.tensors;
-    p.units = (units + 1ull) & ~1ull;  // whole warps iterate together
+    unsigned long long strips = (unsigned long long)a->rows * p.tensors;
+    strips = (strips + 1ull) & ~1ull;  // whole warps iterate together
+    if (strips > 0xffffffffull) return (int)cudaErrorInvalidValue;
+    p.strips = (uint32_t)strips;
     const int threads = 256;
-    unsigned long long want = (p.units * 16 + threads - 1) / threads;
-    // Persistent-ish grid: a multiple of the SM count, 8 resident CTAs per SM.
-    unsigned long long cap = (unsigned long long)sm_count_cached() * 8ull * 4ull;
+    unsigned long long want = (strips * 16 + threads - 1) / threads;
+    // Grid: at most 8 resident CTAs per SM, a multiple of the SM count when capped.
+    unsigned long long cap = (unsigned long long)sm_count_cached() * 8ull;
     unsigned int blocks = (unsigned int)(want < cap ? want : cap);
     if (!blocks) blocks = 1;
     qw_prologue_kernel<<<blocks, threads, 0, stream>>>(p);
