@@ -224,14 +224,24 @@ def run_product(args):
             host_layers.append(sl)
     q_work, k_work = gpu.new_bf16(n_local), gpu.new_bf16(n_local)
     out_local = gpu.new_bf16(n_local)
-    out_full = gpu.new_bf16(n_local * world) if world > 1 else None
     rows_total = w.batch * w.rows
+    fused = world > 1 and args.gather == "fused"
+    out_full = [gpu.new_bf16(n_local * world) for _ in range(2)] if world > 1 else None
+    if fused:
+        for t in out_full:  # collective: maps every rank's buffers over the NVLink peer path
+            gpu.check(lib.qw_gpu_group_bind_output(group, t), "bind_output")
 
     def one_step():
-        for (qt, kt, vt, wqt, wkt) in layers:
+        for i, (qt, kt, vt, wqt, wkt) in enumerate(layers):
+            if fused:
+                # the kernel's epilogue stores this rank's heads into every rank's full
+                # output, then the ranks meet at a barrier; two outputs alternate
+                runner.enqueue(qt, kt, vt, wqt, wkt, q_work=q_work, k_work=k_work, group=group,
+                               full=out_full[i & 1])
+                continue
             runner.enqueue(qt, kt, vt, wqt, wkt, out=out_local, q_work=q_work, k_work=k_work)
             if group:
-                gpu.check(lib.qw_gpu_group_all_gather_heads_bf16(group, out_full, out_local,
+                gpu.check(lib.qw_gpu_group_all_gather_heads_bf16(group, out_full[i & 1], out_local,
                                                                  rows_total, heads_local, 128),
                           "all_gather")
 
@@ -258,11 +268,27 @@ def run_product(args):
         return seconds
 
     timed(one_step, max(args.warmup, 3))
+    # One step (32 layers) is captured once and replayed: the host cost of ~100 op
+    # enqueues per step would otherwise bound short layers at N > 1.
+    step = one_step
+    graph = None
+    if args.graph:
+        gpu.begin()
+        gpu.check(lib.qw_gpu_graph_begin(gpu.handle), "graph begin")
+        one_step()
+        graph = lib.qw_gpu_graph_end(gpu.handle)
+        if not graph:
+            sys.exit("graph capture: " + gpu.error())
+        gpu.submit()
+
+        def step():
+            gpu.check(lib.qw_gpu_graph_launch(gpu.handle, graph), "graph launch")
+        timed(step, 1)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches_before = lib.qw_gpu_kernel_launches(gpu.handle)
-    seconds = timed(one_step, args.steps)
+    seconds = timed(step, args.steps)
     launches = lib.qw_gpu_kernel_launches(gpu.handle) - launches_before
     clocks = sampler.stop() if rank == 0 else None
 
@@ -323,10 +349,14 @@ def run_product(args):
             "config": {"workload": w.name, "batch": w.batch, "rows": w.rows, "heads": w.heads,
                        "head_dim": 128, "layers": w.layers, "text_len": list(w.text_len),
                        "text_pad": w.text_pad,
-                       "parallelism": f"heads/{world}" + (" + NCCL all-gather per layer" if world > 1 else ""),
+                       "parallelism": f"heads/{world}" + (
+                           "" if world == 1 else
+                           " + fused peer-store gather in the attention epilogue + barrier"
+                           if fused else " + NCCL all-gather + interleave per layer"),
                        "l2": "inputs larger than L2: 32 layers x %.0f MB of q,k,v stream through "
                              "each step" % (3 * n_local * 2 / 1e6),
-                       "step": "32 layers x (fused QK-norm+RoPE, block-causal attention)"},
+                       "step": "32 layers x (fused QK-norm+RoPE, block-causal attention)"
+                               + (", replayed from a captured graph" if graph else "")},
             "tflops_per_gpu": value / world,
             "pct_bf16_peak_measured_burst": 100 * value / world / peaks["bf16"],
             "pct_bf16_peak_nominal": 100 * value / world / NOMINAL_BF16_TFLOPS,
@@ -335,6 +365,8 @@ def run_product(args):
             "clocks": clocks, "e2e": e2e,
         }
         print(json.dumps(line), flush=True)
+    if graph:
+        lib.qw_gpu_graph_free(graph)
     if group:
         lib.qw_gpu_group_free(group)
     gpu.close()
@@ -407,6 +439,10 @@ def main():
     ap.add_argument("--workload", type=int, default=3, choices=[2, 3, 4, 5])
     ap.add_argument("--layers", type=int, default=0,
                     help="override the layer count (small captures under a profiler)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: attention epilogue stores to every rank (fused) or NCCL all-gather")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="enqueue every op of every step from the host instead of replaying a graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-e2e", dest="e2e", action="store_false")

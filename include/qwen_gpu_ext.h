@@ -124,6 +124,16 @@ int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name);
 /* Launches enqueued by this context's ops since creation (own kernels only). */
 uint64_t qw_gpu_kernel_launches(const h3_gpu *gpu);
 
+/* Replayable graphs: ops enqueued between begin and end (inside an open chain)
+ * are captured instead of run; qw_gpu_graph_launch replays them with one launch.
+ * The first call of every op kind must have happened before a capture (one-time
+ * kernel attribute set-up is not capturable). */
+typedef struct qw_gpu_graph qw_gpu_graph;
+int qw_gpu_graph_begin(h3_gpu *gpu);
+qw_gpu_graph *qw_gpu_graph_end(h3_gpu *gpu);
+int qw_gpu_graph_launch(h3_gpu *gpu, qw_gpu_graph *graph);
+void qw_gpu_graph_free(qw_gpu_graph *graph);
+
 /* ---- multi-GPU: heads sharded across one process per GPU --------------- */
 typedef struct qw_gpu_group qw_gpu_group;
 #define QW_GPU_GROUP_ID_BYTES 128
@@ -141,6 +151,29 @@ int qw_gpu_group_world(const qw_gpu_group *group);
 int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
                                        const h3_gpu_tensor *local, uint32_t rows,
                                        uint32_t heads_local, uint32_t head_dim);
+
+/* Fused gather.  qw_gpu_group_bind_output (collective) maps every rank's `full`
+ * buffer into every process over the NVLink peer path; after that
+ * qw_gpu_group_attn_block_causal_bf16 runs this rank's heads and its epilogue
+ * stores them into head columns [rank*heads_local, (rank+1)*heads_local) of
+ * the full [batch*rows, world*heads_local*128] output on EVERY rank, followed by
+ * a cross-rank barrier: no landing zone, no interleave pass.
+ * Up to 4 outputs can be bound; alternate between two when a consumer may
+ * still read layer L's output while another rank already stores layer L+1.
+ * Arguments as qw_gpu_attn_block_causal_bf16 with this rank's head counts. */
+int qw_gpu_group_bind_output(qw_gpu_group *group, h3_gpu_tensor *full);
+int qw_gpu_group_barrier(qw_gpu_group *group);
+/* The barrier behind a fused gather runs on the group's own stream so that an
+ * independent next layer need not wait for it.  Before enqueueing a consumer of
+ * `full`, make the context's stream wait for it; h3_gpu_submit waits anyway. */
+int qw_gpu_group_wait_output(qw_gpu_group *group, const h3_gpu_tensor *full);
+int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
+                                        const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                        const h3_gpu_tensor *value,
+                                        const h3_gpu_tensor *kv_limit, uint32_t batch,
+                                        uint32_t rows, uint32_t heads_local,
+                                        uint32_t kv_heads_local, uint32_t head_dim,
+                                        const uint32_t *text_len, uint32_t text_pad, float scale);
 
 #ifdef __cplusplus
 }

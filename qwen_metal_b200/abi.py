@@ -108,12 +108,22 @@ _SIGNATURES = {
     "qw_gpu_tensor_read_async": (C.c_int, [c_gpu, c_tensor, C.c_void_p, size_t]),
     "qw_gpu_set_attention_kernel": (C.c_int, [c_gpu, C.c_char_p]),
     "qw_gpu_kernel_launches": (C.c_uint64, [c_gpu]),
+    "qw_gpu_graph_begin": (C.c_int, [c_gpu]),
+    "qw_gpu_graph_end": (C.c_void_p, [c_gpu]),
+    "qw_gpu_graph_launch": (C.c_int, [c_gpu, C.c_void_p]),
+    "qw_gpu_graph_free": (None, [C.c_void_p]),
     "qw_gpu_group_new_id": (C.c_int, [C.c_void_p, C.c_char_p, size_t]),
     "qw_gpu_group_join": (C.c_void_p, [c_gpu, C.c_void_p, C.c_int, C.c_int, C.c_char_p, size_t]),
     "qw_gpu_group_free": (None, [C.c_void_p]),
     "qw_gpu_group_rank": (C.c_int, [C.c_void_p]),
     "qw_gpu_group_world": (C.c_int, [C.c_void_p]),
     "qw_gpu_group_all_gather_heads_bf16": (C.c_int, [C.c_void_p, c_tensor, c_tensor, u32, u32, u32]),
+    "qw_gpu_group_bind_output": (C.c_int, [C.c_void_p, c_tensor]),
+    "qw_gpu_group_barrier": (C.c_int, [C.c_void_p]),
+    "qw_gpu_group_wait_output": (C.c_int, [C.c_void_p, c_tensor]),
+    "qw_gpu_group_attn_block_causal_bf16": (
+        C.c_int, [C.c_void_p, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32,
+                  u32, C.c_void_p, u32, f32]),
     "qw_dit_prefix_limits": (None, [C.POINTER(Segment), u32, C.c_void_p]),
     "qw_pipe_rope_tables": (
         C.c_int, [c_gpu, u32, u32, u32, C.POINTER(c_tensor), C.POINTER(c_tensor), C.c_char_p, size_t]),

@@ -35,6 +35,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include "../qw_cuda.h"
 
@@ -74,7 +75,8 @@ enum Barrier : int {
     kBarPFull = kBarSFull + 2,            // 2: P_i written (one arrival per warp)
     kBarOFinal = kBarPFull + 2,           // 2: last P V of sub-tile i complete
     kBarDebug = kBarOFinal + 2,           // trace builds: group completion probe
-    kBarCount = kBarDebug + 1
+    kBarEpi = kBarDebug + 1,              // 2: output tile of sub-tile i staged in shared memory
+    kBarCount = kBarEpi + 2
 };
 
 struct __align__(16) SharedControl {
@@ -104,6 +106,11 @@ struct KernelParams {
     uint32_t text_pad;
     float scale_log2;  // scale * log2(e)
     int head_major_out;
+    // Sharded runs: the same rows are stored into every rank's full output
+    // (peer-mapped pointers, plain stores over NVLink).  out_heads_total is the
+    // head count of the destination rows and out_head_offset this rank's first head.
+    __nv_bfloat16 *out_peers[8];
+    uint32_t n_out, out_heads_total, out_head_offset;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -172,6 +179,20 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map,
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// Output tensor maps, one per destination (one on a single GPU, one per rank
+// when the heads are sharded and every rank receives the rows).
+struct OutMaps {
+    CUtensorMap m[8];
+};
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, const void *src, int c0, int c1,
+                                             int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
 
@@ -384,8 +405,9 @@ __device__ __forceinline__ bool tile_skipped(const SharedControl *ctl, int j) {
 // ---------------------------------------------------------------------------
 template <int kPoly>
 __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedControl *ctl,
-                                             int sub, int tid_in_group, int my_limit, uint32_t b,
-                                             uint32_t h, uint32_t row) {
+                                             const OutMaps &maps_out, uint8_t *stage, int sub,
+                                             int tid_in_group, int my_limit, uint32_t b, uint32_t h,
+                                             uint32_t row, uint32_t tile_row0) {
     const int warp_in_group = tid_in_group >> 5;
     const uint32_t lane_base = (uint32_t)(warp_in_group * 32) << 16;
     const uint32_t tmem = ctl->tmem_base;
@@ -523,42 +545,92 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         ++processed;
     }
 
-    // Epilogue: O / l -> bf16 -> global (this thread's row of this head).
-    __nv_bfloat16 *dst = nullptr;
-    if (row < p.q_rows) {
-        size_t index = p.head_major_out
-                           ? (((size_t)b * p.heads + h) * p.q_rows + row) * kHeadDim
-                           : (((size_t)b * p.q_rows + row) * p.heads + h) * kHeadDim;
-        dst = p.out + index;
+    // Epilogue: O / l -> bf16.  Token-major output goes through shared memory (the
+    // dead Q tile of this sub-tile, same swizzled box layout) and leaves as TMA
+    // stores of the whole 128x128 tile, one pair per destination: on a single
+    // GPU that is one coalesced write, with sharded heads the same tile also
+    // goes to every peer's output over NVLink in bulk instead of 64-byte pieces.
+    if (!ok || tile_row0 >= p.q_rows) return;  // gave up, or this sub-tile holds no rows
+    const bool has_row = row < p.q_rows;
+    const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    if (processed > 0) {
+        ok = mbar_wait(ctl, &ctl->bars[kBarOFinal + sub], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarOFinal + sub), 0xffffu);
+        if (!ok) return;
+        tc_fence_after();
+    } else if (!p.head_major_out) {
+        // Nothing was computed for this sub-tile (zeros go out), but its Q load may
+        // still be in flight into the staging area: let it land first.
+        ok = mbar_wait(ctl, &ctl->bars[kBarQFull + sub], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarQFull + sub), 0xfffdu);
+        if (!ok) return;
     }
-    if (processed == 0 || !ok) {
-        if (dst && ok) {
-            uint4 zero = make_uint4(0, 0, 0, 0);
+    if (p.head_major_out) {
+        // (every lane takes part in the warp-collective TMEM loads; only the
+        // stores depend on the row being real)
+        __nv_bfloat16 *dst =
+            p.out + (((size_t)b * p.heads + h) * p.q_rows + (has_row ? row : 0u)) * kHeadDim;
+#pragma unroll 1
+        for (int chunk = 0; chunk < 4; ++chunk) {
+            uint32_t o[32];
+            if (processed > 0) {
+                QW_TMEM_LD32(tmem_o + chunk * 32, o);
+                tmem_wait_ld();
+            }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) reinterpret_cast<uint4 *>(dst)[i] = zero;
+            for (int i = 0; i < 32; i += 8) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (processed > 0) {
+                    v.x = pack_bf16(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                    v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                    v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                    v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                }
+                if (has_row) reinterpret_cast<uint4 *>(dst + chunk * 32)[i >> 3] = v;
+            }
         }
         return;
     }
-    ok = mbar_wait(ctl, &ctl->bars[kBarOFinal + sub], 0, p.status,
-                   (1u << 16) | (uint32_t)(kBarOFinal + sub), 0xffffu);
-    if (!ok) return;
-    tc_fence_after();
-    const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    {
+        // Row r of the tile: two 128-byte lines (columns 0..63 and 64..127, one
+        // half tile apart), 16-byte chunks XOR-swizzled by the row like TMA does.
+        const int r = tid_in_group;
+        uint8_t *line = stage + r * 128;
+        const int sw = r & 7;
 #pragma unroll 1
-    for (int chunk = 0; chunk < 4; ++chunk) {
-        uint32_t o[32];
-        QW_TMEM_LD32(tmem_o + chunk * 32, o);
-        tmem_wait_ld();
-        if (dst) {
+        for (int chunk = 0; chunk < 4; ++chunk) {
+            uint32_t o[32];
+            if (processed > 0) {
+                QW_TMEM_LD32(tmem_o + chunk * 32, o);
+                tmem_wait_ld();
+            }
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                reinterpret_cast<uint4 *>(dst + chunk * 32)[i >> 3] = v;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (processed > 0) {
+                    v.x = pack_bf16(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                    v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                    v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                    v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                }
+                const int c = chunk * 4 + (i >> 3);  // 16-byte chunk of the 256-byte row
+                *reinterpret_cast<uint4 *>(line + (c >> 3) * kHalfTileBytes + (((c & 7) ^ sw) << 4)) = v;
             }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> TMA reads
+        __syncwarp();
+        if ((tid_in_group & 31) == 0) mbar_arrive(&ctl->bars[kBarEpi + sub]);
+        if (tid_in_group == 0) {
+            if (!mbar_wait(ctl, &ctl->bars[kBarEpi + sub], 0, p.status,
+                           (1u << 16) | (uint32_t)(kBarEpi + sub), 0xfffcu))
+                return;
+            const int col = (int)((p.out_head_offset + h) * kHeadDim);
+            for (uint32_t d = 0; d < p.n_out; ++d) {
+                tma_store_3d(&maps_out.m[d], stage, col, (int)tile_row0, (int)b);
+                tma_store_3d(&maps_out.m[d], stage + kHalfTileBytes, col + 64, (int)tile_row0, (int)b);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
     }
 }
@@ -754,7 +826,8 @@ template <int kPoly>
 __global__ void __launch_bounds__(kThreads, 1)
 qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
                      const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const KernelParams p) {
+                     const __grid_constant__ CUtensorMap map_v,
+                     const __grid_constant__ OutMaps maps_out, const KernelParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *smem_q = smem;
@@ -781,6 +854,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_init(&ctl->bars[kBarSFull + i], 1);
             mbar_init(&ctl->bars[kBarPFull + i], kTileM / 32);
             mbar_init(&ctl->bars[kBarOFinal + i], 1);
+            mbar_init(&ctl->bars[kBarEpi + i], kTileM / 32);
         }
         mbar_init(&ctl->bars[kBarDebug], 1);
         ctl->abort_flag = 0;
@@ -842,7 +916,8 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
 
     if (tid < kSoftmaxThreads) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-        softmax_role<kPoly>(p, ctl, sub, tid_in_group, my_limit, b, h, my_row);
+        softmax_role<kPoly>(p, ctl, maps_out, smem_q + (size_t)sub * kTileBytes, sub, tid_in_group,
+                            my_limit, b, h, my_row, row0 + (uint32_t)sub * kTileM);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     }
@@ -941,7 +1016,7 @@ void trace_dump(cudaStream_t stream) {
 }
 #endif
 
-typedef void (*AttnKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
+typedef void (*AttnKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const OutMaps,
                            const KernelParams);
 
 // How many of every 4 score pairs take the polynomial exp2 (QW_CUDA_EXP_POLY=0..4
@@ -1002,8 +1077,29 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     p.text_pad = a->text_pad;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.head_major_out = a->head_major_out;
+    if (a->n_out_peers > 0) {
+        if (a->n_out_peers > 8 || a->head_major_out) return (int)cudaErrorInvalidValue;
+        p.n_out = a->n_out_peers;
+        for (uint32_t d = 0; d < p.n_out; ++d) {
+            if ((uintptr_t)a->out_peers[d] & 15u) return (int)cudaErrorMisalignedAddress;
+            p.out_peers[d] = static_cast<__nv_bfloat16 *>(a->out_peers[d]);
+        }
+        p.out_heads_total = a->out_heads_total;
+        p.out_head_offset = a->out_head_offset;
+    } else {
+        p.n_out = 1;
+        p.out_peers[0] = p.out;
+        p.out_heads_total = a->heads;
+        p.out_head_offset = 0;
+    }
+    OutMaps maps_out;
+    memset(&maps_out, 0, sizeof(maps_out));
+    if (!p.head_major_out)
+        for (uint32_t d = 0; d < p.n_out; ++d)
+            if ((rc = make_map(&maps_out.m[d], p.out_peers[d], a->batch, a->q_rows, p.out_heads_total)))
+                return rc;
     dim3 grid((a->q_rows + 2 * kTileM - 1) / (2 * kTileM), a->heads, a->batch);
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, p);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, maps_out, p);
     rc = (int)cudaGetLastError();
 #ifdef QW_ATTN_TRACE
     if (p.trace && !rc) trace_dump(stream);

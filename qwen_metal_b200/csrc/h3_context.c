@@ -80,6 +80,10 @@ int qw_require_dtype(h3_gpu *gpu, const h3_gpu_tensor *tensor, size_t elements,
 
 void qw_count_launch(h3_gpu *gpu, int rc, const char *what) {
     if (rc == 0) {
+        if (gpu->capturing) {
+            gpu->capture_launches++; /* credited on every replay of the graph */
+            return;
+        }
         gpu->stats.direct_dispatches++;
         gpu->kernel_launches++;
     } else {
@@ -194,6 +198,7 @@ void h3_gpu_free(h3_gpu *gpu) {
     if (gpu->status_host) cudaFreeHost(gpu->status_host);
     if (gpu->chain_start) cudaEventDestroy(gpu->chain_start);
     if (gpu->chain_stop) cudaEventDestroy(gpu->chain_stop);
+    if (gpu->aux_joined) cudaEventDestroy(gpu->aux_joined);
     if (gpu->stream) cudaStreamDestroy(gpu->stream);
     cudaGetLastError();
     free(gpu);
@@ -408,12 +413,24 @@ int h3_gpu_continue(h3_gpu *gpu) {
 
 int h3_gpu_submit(h3_gpu *gpu) {
     if (!gpu || !gpu->chain_open || !qw_bind(gpu)) return 0;
+    if (gpu->capturing) {
+        qw_set_error(gpu, "h3_gpu_submit() inside a graph capture; call qw_gpu_graph_end() first");
+        return 0;
+    }
     gpu->chain_open = 0;
     double commit_time = qw_now();
+    if (gpu->aux_stream) {
+        /* Work a multi-GPU group put on its communication stream belongs to the
+         * chain: join it before the stop event. */
+        if (!gpu->aux_joined) cudaEventCreateWithFlags(&gpu->aux_joined, cudaEventDisableTiming);
+        if (gpu->aux_joined && cudaEventRecord(gpu->aux_joined, gpu->aux_stream) == cudaSuccess)
+            cudaStreamWaitEvent(gpu->stream, gpu->aux_joined, 0);
+    }
     cudaEventRecord(gpu->chain_stop, gpu->stream);
     cudaMemcpyAsync(gpu->status_host, gpu->status_dev, QWCU_STATUS_WORDS * sizeof(uint32_t),
                     cudaMemcpyDeviceToHost, gpu->stream);
     cudaError_t code = cudaStreamSynchronize(gpu->stream);
+    if (code == cudaSuccess && gpu->aux_stream) code = cudaStreamSynchronize(gpu->aux_stream);
     double complete_time = qw_now();
     if (code != cudaSuccess) {
         qw_set_error(gpu, "CUDA command failed: %s", cudaGetErrorString(code));
@@ -439,6 +456,76 @@ int h3_gpu_submit(h3_gpu *gpu) {
     gpu->stats.command_encode_seconds += commit_time - gpu->chain_start_wall;
     gpu->stats.command_wait_seconds += complete_time - commit_time;
     return 1;
+}
+
+/* ---- replayable graphs (no counterpart in the reference) ------------------
+ * The ops enqueued between begin and end are captured instead of run; the graph
+ * replays them with one launch, which takes the per-op host cost out of short
+ * layers (at 8 GPUs a layer is ~70 us of device time). */
+int qw_gpu_graph_begin(h3_gpu *gpu) {
+    if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
+    if (gpu->capturing) {
+        qw_set_error(gpu, "graph capture is already active");
+        return 0;
+    }
+    if (!qw_cuda_ok(gpu, cudaStreamBeginCapture(gpu->stream, cudaStreamCaptureModeRelaxed),
+                    "graph capture begin"))
+        return 0;
+    gpu->capturing = 1;
+    gpu->capture_seq++;
+    gpu->capture_launches = 0;
+    return 1;
+}
+
+qw_gpu_graph *qw_gpu_graph_end(h3_gpu *gpu) {
+    if (!gpu || !gpu->capturing || !qw_bind(gpu)) return NULL;
+    if (gpu->aux_stream) { /* join the communication stream back into the capture */
+        if (!gpu->aux_joined) cudaEventCreateWithFlags(&gpu->aux_joined, cudaEventDisableTiming);
+        if (gpu->aux_joined && cudaEventRecord(gpu->aux_joined, gpu->aux_stream) == cudaSuccess)
+            cudaStreamWaitEvent(gpu->stream, gpu->aux_joined, 0);
+    }
+    cudaGraph_t graph = NULL;
+    cudaError_t code = cudaStreamEndCapture(gpu->stream, &graph);
+    gpu->capturing = 0;
+    if (code != cudaSuccess || !graph) {
+        qw_set_error(gpu, "graph capture end: %s", cudaGetErrorString(code));
+        cudaGetLastError();
+        return NULL;
+    }
+    qw_gpu_graph *handle = calloc(1, sizeof(*handle));
+    if (handle) code = cudaGraphInstantiate(&handle->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (!handle || code != cudaSuccess) {
+        qw_set_error(gpu, "graph instantiate: %s", cudaGetErrorString(code));
+        cudaGetLastError();
+        free(handle);
+        return NULL;
+    }
+    handle->owner = gpu;
+    handle->kernel_launches = gpu->capture_launches;
+    return handle;
+}
+
+int qw_gpu_graph_launch(h3_gpu *gpu, qw_gpu_graph *graph) {
+    if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
+    if (!graph || graph->owner != gpu || gpu->capturing) {
+        qw_set_error(gpu, "graph launch: no graph of this context");
+        return 0;
+    }
+    if (!qw_cuda_ok(gpu, cudaGraphLaunch(graph->exec, gpu->stream), "graph launch")) {
+        gpu->chain_failed = 1;
+        return 0;
+    }
+    gpu->stats.direct_dispatches += graph->kernel_launches;
+    gpu->kernel_launches += graph->kernel_launches;
+    return 1;
+}
+
+void qw_gpu_graph_free(qw_gpu_graph *graph) {
+    if (!graph) return;
+    if (graph->owner) qw_bind(graph->owner);
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    free(graph);
 }
 
 /* reference h3_gpu.m:1049-1053 */

@@ -59,6 +59,13 @@ typedef struct {
     float scale;
     int scale_in_q; /* h3 causal variant: q' = bf16(q*scale), scores unscaled */
     int head_major_out;
+    /* Sharded heads (n_out_peers > 0, sm100 kernel only): instead of `out`, the
+     * rows are stored at head columns [out_head_offset, out_head_offset + heads)
+     * of [batch][q_rows][out_heads_total][128] in each of the peer-mapped buffers. */
+    void *out_peers[8];
+    uint32_t n_out_peers;
+    uint32_t out_heads_total;
+    uint32_t out_head_offset;
     uint32_t *status; /* QWCU_STATUS_WORDS device words, zero when healthy */
 } qwcu_attn_args;
 

@@ -15,12 +15,14 @@
 
 typedef struct ncclComm *nccl_comm_t;
 typedef struct { char internal[QW_GPU_GROUP_ID_BYTES]; } nccl_unique_id;
-enum { NCCL_BFLOAT16 = 9 }; /* ncclDataType_t value of ncclBfloat16 */
+enum { NCCL_UINT8 = 1, NCCL_FLOAT32 = 7, NCCL_BFLOAT16 = 9 }; /* ncclDataType_t values */
+enum { NCCL_SUM = 0 };                                      /* ncclRedOp_t */
 
 typedef int (*nccl_get_unique_id_fn)(nccl_unique_id *);
 typedef int (*nccl_comm_init_rank_fn)(nccl_comm_t *, int, nccl_unique_id, int);
 typedef int (*nccl_comm_destroy_fn)(nccl_comm_t);
 typedef int (*nccl_all_gather_fn)(const void *, void *, size_t, int, nccl_comm_t, cudaStream_t);
+typedef int (*nccl_all_reduce_fn)(const void *, void *, size_t, int, int, nccl_comm_t, cudaStream_t);
 typedef const char *(*nccl_get_error_string_fn)(int);
 
 static struct {
@@ -29,6 +31,7 @@ static struct {
     nccl_comm_init_rank_fn comm_init_rank;
     nccl_comm_destroy_fn comm_destroy;
     nccl_all_gather_fn all_gather;
+    nccl_all_reduce_fn all_reduce;
     nccl_get_error_string_fn get_error_string;
 } g_nccl;
 
@@ -46,9 +49,10 @@ static int nccl_bind(char *error, size_t error_size) {
     g_nccl.comm_init_rank = (nccl_comm_init_rank_fn)dlsym(handle, "ncclCommInitRank");
     g_nccl.comm_destroy = (nccl_comm_destroy_fn)dlsym(handle, "ncclCommDestroy");
     g_nccl.all_gather = (nccl_all_gather_fn)dlsym(handle, "ncclAllGather");
+    g_nccl.all_reduce = (nccl_all_reduce_fn)dlsym(handle, "ncclAllReduce");
     g_nccl.get_error_string = (nccl_get_error_string_fn)dlsym(handle, "ncclGetErrorString");
     if (!g_nccl.get_unique_id || !g_nccl.comm_init_rank || !g_nccl.comm_destroy ||
-        !g_nccl.all_gather || !g_nccl.get_error_string) {
+        !g_nccl.all_gather || !g_nccl.all_reduce || !g_nccl.get_error_string) {
         if (error && error_size) snprintf(error, error_size, "NCCL library lacks a required symbol");
         dlclose(handle);
         memset(&g_nccl, 0, sizeof(g_nccl));
@@ -58,6 +62,10 @@ static int nccl_bind(char *error, size_t error_size) {
     return 1;
 }
 
+#define QW_GROUP_MAX_WORLD 8
+#define QW_IPC_HANDLE_BYTES 64
+#define QW_GROUP_MAX_BOUND 4
+
 struct qw_gpu_group {
     h3_gpu *gpu;
     nccl_comm_t comm;
@@ -65,6 +73,21 @@ struct qw_gpu_group {
     void *staging; /* [world][rows][slice] landing zone of the collective */
     size_t staging_bytes;
     int sm_count;
+    /* Fused gather: every rank's full output buffer mapped into this process. */
+    unsigned char *exchange; /* device: world * 64-byte IPC handles, then one float */
+    /* Up to QW_GROUP_MAX_BOUND outputs can be bound at once (a consumer that is
+     * still reading layer L's output on one rank must not see another rank's
+     * layer L+1 stores: alternate between two bound buffers). */
+    h3_gpu_tensor *bound[QW_GROUP_MAX_BOUND];
+    void *peer_out[QW_GROUP_MAX_BOUND][QW_GROUP_MAX_WORLD];
+    /* The barrier that completes a fused gather runs on its own stream so the
+     * next (independent) layer does not wait for it; slot_done[b] marks the
+     * last barrier that covered bound output b. */
+    cudaStream_t comm_stream;
+    cudaEvent_t kernel_done;
+    cudaEvent_t slot_done[QW_GROUP_MAX_BOUND];
+    int slot_pending[QW_GROUP_MAX_BOUND];
+    uint32_t slot_capture[QW_GROUP_MAX_BOUND]; /* capture the slot's event belongs to (0 = none) */
 };
 
 int qw_gpu_group_new_id(void *id_bytes, char *error, size_t error_size) {
@@ -102,6 +125,24 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
         free(group);
         return NULL;
     }
+    if (cudaMalloc((void **)&group->exchange, QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES + 16) !=
+        cudaSuccess) {
+        if (error && error_size) snprintf(error, error_size, "group: exchange buffer allocation failed");
+        g_nccl.comm_destroy(group->comm);
+        free(group);
+        return NULL;
+    }
+    cudaMemset(group->exchange, 0, QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES + 16);
+    int ok = cudaStreamCreateWithFlags(&group->comm_stream, cudaStreamNonBlocking) == cudaSuccess &&
+             cudaEventCreateWithFlags(&group->kernel_done, cudaEventDisableTiming) == cudaSuccess;
+    for (int b = 0; ok && b < QW_GROUP_MAX_BOUND; b++)
+        ok = cudaEventCreateWithFlags(&group->slot_done[b], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
+        if (error && error_size) snprintf(error, error_size, "group: stream/event creation failed");
+        qw_gpu_group_free(group);
+        return NULL;
+    }
+    gpu->aux_stream = group->comm_stream;
     return group;
 }
 
@@ -110,8 +151,19 @@ void qw_gpu_group_free(qw_gpu_group *group) {
     if (group->gpu) {
         qw_bind(group->gpu);
         cudaStreamSynchronize(group->gpu->stream);
+        if (group->comm_stream) cudaStreamSynchronize(group->comm_stream);
+        if (group->gpu->aux_stream == group->comm_stream) group->gpu->aux_stream = NULL;
     }
+    if (group->kernel_done) cudaEventDestroy(group->kernel_done);
+    for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
+        if (group->slot_done[b]) cudaEventDestroy(group->slot_done[b]);
+    if (group->comm_stream) cudaStreamDestroy(group->comm_stream);
+    for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
+        for (int r = 0; r < group->world && r < QW_GROUP_MAX_WORLD; r++)
+            if (group->peer_out[b][r] && r != group->rank)
+                cudaIpcCloseMemHandle(group->peer_out[b][r]);
     if (group->staging) cudaFree(group->staging);
+    if (group->exchange) cudaFree(group->exchange);
     if (group->comm) g_nccl.comm_destroy(group->comm);
     free(group);
 }
@@ -163,4 +215,162 @@ int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
                                 (uint32_t)group->world, group->sm_count, gpu->stream);
     qw_count_launch(gpu, rc, "head interleave");
     return rc == 0;
+}
+
+/* Map every rank's `full` output buffer into this process (CUDA IPC over the
+ * NVLink peer path) so the attention kernel can store its head columns straight
+ * into all of them.  Collective: every rank calls it with its own tensor of the
+ * same size.  The handles travel through the group's own NCCL communicator. */
+int qw_gpu_group_bind_output(qw_gpu_group *group, h3_gpu_tensor *full) {
+    if (!group) return 0;
+    h3_gpu *gpu = group->gpu;
+    if (!full || full->dtype != H3_GPU_BF16 || full->owner != gpu) {
+        qw_set_error(gpu, "group bind: output tensor is absent or not BF16");
+        return 0;
+    }
+    if (group->world > QW_GROUP_MAX_WORLD) {
+        qw_set_error(gpu, "group bind: at most %d ranks", QW_GROUP_MAX_WORLD);
+        return 0;
+    }
+    if (!qw_bind(gpu)) return 0;
+    int slot_index = -1;
+    for (int b = 0; b < QW_GROUP_MAX_BOUND && slot_index < 0; b++)
+        if (!group->bound[b]) slot_index = b;
+    if (slot_index < 0) {
+        qw_set_error(gpu, "group bind: at most %d outputs can be bound", QW_GROUP_MAX_BOUND);
+        return 0;
+    }
+    void **peers = group->peer_out[slot_index];
+    cudaIpcMemHandle_t mine;
+    if (!qw_cuda_ok(gpu, cudaIpcGetMemHandle(&mine, full->dev), "cudaIpcGetMemHandle")) return 0;
+    unsigned char host[QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES];
+    unsigned char *slot = group->exchange + (size_t)group->rank * QW_IPC_HANDLE_BYTES;
+    if (!qw_cuda_ok(gpu, cudaMemcpyAsync(slot, &mine, QW_IPC_HANDLE_BYTES, cudaMemcpyHostToDevice,
+                                         gpu->stream), "handle upload"))
+        return 0;
+    int rc = g_nccl.all_gather(slot, group->exchange, QW_IPC_HANDLE_BYTES, NCCL_UINT8, group->comm,
+                               gpu->stream);
+    if (rc) {
+        qw_set_error(gpu, "ncclAllGather (handles): %s", g_nccl.get_error_string(rc));
+        return 0;
+    }
+    if (!qw_cuda_ok(gpu, cudaMemcpyAsync(host, group->exchange,
+                                         (size_t)group->world * QW_IPC_HANDLE_BYTES,
+                                         cudaMemcpyDeviceToHost, gpu->stream), "handle download") ||
+        !qw_cuda_ok(gpu, cudaStreamSynchronize(gpu->stream), "handle exchange"))
+        return 0;
+    for (int r = 0; r < group->world; r++) {
+        if (r == group->rank) {
+            peers[r] = full->dev;
+            continue;
+        }
+        cudaIpcMemHandle_t theirs;
+        memcpy(&theirs, host + (size_t)r * QW_IPC_HANDLE_BYTES, QW_IPC_HANDLE_BYTES);
+        if (!qw_cuda_ok(gpu, cudaIpcOpenMemHandle(&peers[r], theirs, cudaIpcMemLazyEnablePeerAccess),
+                        "cudaIpcOpenMemHandle"))
+            return 0;
+    }
+    group->bound[slot_index] = full;
+    return 1;
+}
+
+/* Cross-rank barrier on the context's stream: when it completes on a rank,
+ * every rank has finished the work it enqueued before its own barrier. */
+int qw_gpu_group_barrier(qw_gpu_group *group) {
+    if (!group) return 0;
+    h3_gpu *gpu = group->gpu;
+    if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
+    if (group->world == 1) return 1;
+    float *word = (float *)(group->exchange + QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES);
+    int rc = g_nccl.all_reduce(word, word, 1, NCCL_FLOAT32, NCCL_SUM, group->comm, gpu->stream);
+    if (rc) {
+        qw_set_error(gpu, "ncclAllReduce (barrier): %s", g_nccl.get_error_string(rc));
+        gpu->chain_failed = 1;
+        return 0;
+    }
+    return 1;
+}
+
+/* Sharded block-causal attention fused with the gather: this rank computes its
+ * heads and the kernel's epilogue stores them into head columns
+ * [rank*heads_local, (rank+1)*heads_local) of the bound `full` output of EVERY
+ * rank (plain stores to peer-mapped memory), then the ranks meet at a barrier.
+ * After it, `full` [batch*rows, world*heads_local*128] is complete everywhere. */
+int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
+                                        const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                        const h3_gpu_tensor *value,
+                                        const h3_gpu_tensor *kv_limit, uint32_t batch,
+                                        uint32_t rows, uint32_t heads_local,
+                                        uint32_t kv_heads_local, uint32_t head_dim,
+                                        const uint32_t *text_len, uint32_t text_pad, float scale) {
+    if (!group) return 0;
+    h3_gpu *gpu = group->gpu;
+    int slot_index = -1;
+    for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
+        if (full && group->bound[b] == full) slot_index = b;
+    if (slot_index < 0) {
+        qw_set_error(gpu, "group attention: output is not a tensor bound with "
+                          "qw_gpu_group_bind_output");
+        return 0;
+    }
+    size_t full_count = (size_t)batch * rows * heads_local * head_dim * (size_t)group->world;
+    if (!qw_require_dtype(gpu, full, full_count, H3_GPU_BF16, "group attention output")) return 0;
+    qwcu_attn_args args;
+    if (!qw_prepare_block_causal(gpu, &args, NULL, query, key, value, kv_limit, batch, rows,
+                                 heads_local, kv_heads_local, head_dim, text_len, text_pad, scale))
+        return 0;
+    args.out = full->dev;
+    args.n_out_peers = (uint32_t)group->world;
+    for (int r = 0; r < group->world; r++) args.out_peers[r] = group->peer_out[slot_index][r];
+    args.out_heads_total = heads_local * (uint32_t)group->world;
+    args.out_head_offset = heads_local * (uint32_t)group->rank;
+    /* Earlier stores into this output (from any rank) were covered by the barrier
+     * recorded in slot_done; a new round of stores must not start before it. */
+    /* (An event recorded outside the current graph capture belongs to work that is
+     * complete before the graph can run: nothing to wait for.) */
+    const uint32_t capture_now = gpu->capturing ? gpu->capture_seq : 0;
+    if (group->slot_pending[slot_index] && group->slot_capture[slot_index] == capture_now &&
+        !qw_cuda_ok(gpu, cudaStreamWaitEvent(gpu->stream, group->slot_done[slot_index], 0),
+                    "group attention (slot wait)"))
+        return 0;
+    if (!qw_launch_attention(gpu, &args, "group attention")) return 0;
+    if (group->world == 1) return 1;
+    /* The barrier runs on the communication stream, behind this kernel. */
+    if (!qw_cuda_ok(gpu, cudaEventRecord(group->kernel_done, gpu->stream), "group attention") ||
+        !qw_cuda_ok(gpu, cudaStreamWaitEvent(group->comm_stream, group->kernel_done, 0),
+                    "group attention"))
+        return 0;
+    float *word = (float *)(group->exchange + QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES);
+    int rc = g_nccl.all_reduce(word, word, 1, NCCL_FLOAT32, NCCL_SUM, group->comm,
+                               group->comm_stream);
+    if (rc) {
+        qw_set_error(gpu, "ncclAllReduce (barrier): %s", g_nccl.get_error_string(rc));
+        gpu->chain_failed = 1;
+        return 0;
+    }
+    if (!qw_cuda_ok(gpu, cudaEventRecord(group->slot_done[slot_index], group->comm_stream),
+                    "group attention"))
+        return 0;
+    group->slot_pending[slot_index] = 1;
+    group->slot_capture[slot_index] = capture_now;
+    return 1;
+}
+
+/* Make the context's stream wait until `full` (a bound output) is complete on
+ * this rank, i.e. until the barrier behind the last fused gather into it has
+ * passed.  Call it before enqueueing a consumer of `full`; h3_gpu_submit waits
+ * for every outstanding barrier by itself. */
+int qw_gpu_group_wait_output(qw_gpu_group *group, const h3_gpu_tensor *full) {
+    if (!group) return 0;
+    h3_gpu *gpu = group->gpu;
+    for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
+        if (full && group->bound[b] == full) {
+            if (!group->slot_pending[b]) return 1;
+            if (group->slot_capture[b] != (gpu->capturing ? gpu->capture_seq : 0)) return 1;
+            return qw_bind(gpu) &&
+                   qw_cuda_ok(gpu, cudaStreamWaitEvent(gpu->stream, group->slot_done[b], 0),
+                              "group wait");
+        }
+    qw_set_error(gpu, "group wait: output is not a tensor bound with qw_gpu_group_bind_output");
+    return 0;
 }

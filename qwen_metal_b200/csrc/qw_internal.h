@@ -27,9 +27,22 @@ struct h3_gpu {
     uint32_t *status_dev;  /* QWCU_STATUS_WORDS words, zero when healthy */
     uint32_t *status_host; /* pinned mirror */
     int attn_kernel;
+    /* A multi-GPU group's communication stream; submit waits for it too. */
+    cudaStream_t aux_stream;
+    cudaEvent_t aux_joined;
+    /* Stream capture into a replayable graph (qw_gpu_graph_*). */
+    int capturing;
+    uint32_t capture_seq;      /* identifies the capture an event was recorded in */
+    uint64_t capture_launches; /* kernel launches counted since capture began */
     /* Scratch for the pre-scaled query of the h3 causal variant; grows on demand. */
     void *scratch;
     size_t scratch_bytes;
+};
+
+struct qw_gpu_graph {
+    h3_gpu *owner;
+    cudaGraphExec_t exec;
+    uint64_t kernel_launches;
 };
 
 struct h3_gpu_tensor {
@@ -52,5 +65,12 @@ int qw_require_dtype(h3_gpu *gpu, const h3_gpu_tensor *tensor, size_t elements,
 void *qw_scratch(h3_gpu *gpu, size_t bytes);
 void qw_count_launch(h3_gpu *gpu, int rc, const char *what);
 double qw_now(void);
+int qw_launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what);
+int qw_prepare_block_causal(h3_gpu *gpu, qwcu_attn_args *args, h3_gpu_tensor *output,
+                            const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                            const h3_gpu_tensor *value, const h3_gpu_tensor *kv_limit,
+                            uint32_t batch, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                            uint32_t head_dim, const uint32_t *text_len, uint32_t text_pad,
+                            float scale);
 
 #endif

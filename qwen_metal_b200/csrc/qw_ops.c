@@ -151,12 +151,16 @@ int qw_gpu_qk_norm_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *k
 
 /* ---- attention ops ------------------------------------------------------- */
 
-static int launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what) {
+int qw_launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what) {
     if (!qw_bind(gpu)) return 0;
     args->status = gpu->status_dev;
     int scalar = gpu->attn_kernel == QW_ATTN_SCALAR;
     /* Degenerate scales cannot ride the exp2-domain fast path. */
     if (!(args->scale > 0.0f) || !isfinite(args->scale)) scalar = 1;
+    if (scalar && args->n_out_peers) {
+        qw_set_error(gpu, "%s: sharded output needs the sm100 kernel and a positive finite scale", what);
+        return 0;
+    }
     if (!scalar && args->scale_in_q) {
         /* h3 causal variant: q' = bf16(q * scale) into scratch, scores unscaled
          * (h3_shaders.metal:4396-4402). */
@@ -210,7 +214,7 @@ int qw_gpu_flash_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tens
     args.heads = heads;
     args.kv_heads = heads;
     args.scale = scale;
-    return launch_attention(gpu, &args, "flash SDPA");
+    return qw_launch_attention(gpu, &args, "flash SDPA");
 }
 
 /* reference h3_gpu.m:5791-5844 */
@@ -247,7 +251,7 @@ int qw_gpu_flash_sdpa_prefix_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_g
     args.heads = heads;
     args.kv_heads = kv_heads;
     args.scale = scale;
-    return launch_attention(gpu, &args, "flash SDPA prefix");
+    return qw_launch_attention(gpu, &args, "flash SDPA prefix");
 }
 
 /* reference h3_gpu.m:5972-6054 */
@@ -280,7 +284,7 @@ int qw_gpu_sdpa_rect_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tenso
     args.heads = heads;
     args.kv_heads = heads;
     args.scale = scale;
-    return launch_attention(gpu, &args, "Rect SDPA");
+    return qw_launch_attention(gpu, &args, "Rect SDPA");
 }
 
 static int gqa_causal(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
@@ -321,7 +325,7 @@ static int gqa_causal(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *q
     args.kv_heads = kv_heads;
     args.scale = scale;
     args.scale_in_q = scale_in_q;
-    return launch_attention(gpu, &args, label);
+    return qw_launch_attention(gpu, &args, label);
 }
 
 /* reference h3_gpu.m:4642-4693 */
@@ -376,7 +380,7 @@ static int sdpa_square(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *
     args.kv_heads = heads;
     args.scale = scale;
     args.head_major_out = head_major_out;
-    return launch_attention(gpu, &args, "SDPA");
+    return qw_launch_attention(gpu, &args, "SDPA");
 }
 
 int h3_gpu_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
@@ -392,14 +396,14 @@ int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *output,
     return sdpa_square(gpu, output, query, key, value, sequence, heads, head_dim, scale, 1);
 }
 
-/* NEW: batched block-causal attention with key padding. */
-int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
-                                  const h3_gpu_tensor *query, const h3_gpu_tensor *key,
-                                  const h3_gpu_tensor *value, const h3_gpu_tensor *kv_limit,
-                                  uint32_t batch, uint32_t rows, uint32_t heads,
-                                  uint32_t kv_heads, uint32_t head_dim,
-                                  const uint32_t *text_len, uint32_t text_pad, float scale) {
-    if (!gpu) return 0;
+/* Validation + argument block of the batched block-causal op; `output` may be
+ * NULL when the caller provides the destinations itself (sharded heads). */
+int qw_prepare_block_causal(h3_gpu *gpu, qwcu_attn_args *args, h3_gpu_tensor *output,
+                            const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                            const h3_gpu_tensor *value, const h3_gpu_tensor *kv_limit,
+                            uint32_t batch, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                            uint32_t head_dim, const uint32_t *text_len, uint32_t text_pad,
+                            float scale) {
     if (head_dim != 128 || !heads || !kv_heads || heads % kv_heads || !batch || batch > 8) {
         qw_set_error(gpu, "block-causal attention: unsupported geometry");
         return 0;
@@ -410,7 +414,8 @@ int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
         !qw_require_dtype(gpu, query, q_count, H3_GPU_BF16, "block-causal attention query") ||
         !qw_require_dtype(gpu, key, kv_count, H3_GPU_BF16, "block-causal attention key") ||
         !qw_require_dtype(gpu, value, kv_count, H3_GPU_BF16, "block-causal attention value") ||
-        !qw_require_dtype(gpu, output, q_count, H3_GPU_BF16, "block-causal attention output"))
+        (output &&
+         !qw_require_dtype(gpu, output, q_count, H3_GPU_BF16, "block-causal attention output")))
         return 0;
     int per_batch = 0;
     if (kv_limit) {
@@ -431,23 +436,41 @@ int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
             }
     }
     if (!qw_require_command(gpu)) return 0;
-    qwcu_attn_args args;
-    memset(&args, 0, sizeof(args));
-    args.q = query->dev;
-    args.k = key->dev;
-    args.v = value->dev;
-    args.out = output->dev;
-    args.kv_limit = kv_limit ? kv_limit->dev : NULL;
-    args.per_batch_limits = per_batch;
-    args.batch = batch;
-    args.q_rows = rows;
-    args.kv_rows = rows;
-    args.heads = heads;
-    args.kv_heads = kv_heads;
+    memset(args, 0, sizeof(*args));
+    args->q = query->dev;
+    args->k = key->dev;
+    args->v = value->dev;
+    args->out = output ? output->dev : NULL;
+    args->kv_limit = kv_limit ? kv_limit->dev : NULL;
+    args->per_batch_limits = per_batch;
+    args->batch = batch;
+    args->q_rows = rows;
+    args->kv_rows = rows;
+    args->heads = heads;
+    args->kv_heads = kv_heads;
     if (text_len && text_pad) {
-        for (uint32_t b = 0; b < batch; b++) args.text_len[b] = text_len[b];
-        args.text_pad = text_pad;
+        for (uint32_t b = 0; b < batch; b++) args->text_len[b] = text_len[b];
+        args->text_pad = text_pad;
     }
-    args.scale = scale;
-    return launch_attention(gpu, &args, "block-causal attention");
+    args->scale = scale;
+    return 1;
+}
+
+/* NEW: batched block-causal attention with key padding. */
+int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                  const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                  const h3_gpu_tensor *value, const h3_gpu_tensor *kv_limit,
+                                  uint32_t batch, uint32_t rows, uint32_t heads,
+                                  uint32_t kv_heads, uint32_t head_dim,
+                                  const uint32_t *text_len, uint32_t text_pad, float scale) {
+    if (!gpu) return 0;
+    if (!output) {
+        qw_set_error(gpu, "block-causal attention output tensor is absent or too small");
+        return 0;
+    }
+    qwcu_attn_args args;
+    if (!qw_prepare_block_causal(gpu, &args, output, query, key, value, kv_limit, batch, rows,
+                                 heads, kv_heads, head_dim, text_len, text_pad, scale))
+        return 0;
+    return qw_launch_attention(gpu, &args, "block-causal attention");
 }

@@ -153,9 +153,12 @@ class LayerRunner:
         self.text_len = (np.asarray(w.text_len, dtype=np.uint32) if w.text_pad else None)
         self.out = gpu.new_bf16(n)
 
-    def enqueue(self, q, k, v, wq=None, wk=None, out=None, q_work=None, k_work=None):
+    def enqueue(self, q, k, v, wq=None, wk=None, out=None, q_work=None, k_work=None,
+                group=None, full=None):
         """One layer: [fused QK-norm + RoPE] then block-causal attention.  With
-        q_work/k_work the prologue writes there and leaves q, k untouched."""
+        q_work/k_work the prologue writes there and leaves q, k untouched.  With a
+        multi-GPU group and a bound `full` output the attention kernel stores this
+        rank's heads into every rank's `full` (fused gather)."""
         g, w, lib = self.gpu, self.w, self.gpu.lib
         out = out or self.out
         if w.prologue:
@@ -166,6 +169,11 @@ class LayerRunner:
                     "qk_norm_rope")
             q, k = qo, ko
         tl = abi._ptr(self.text_len) if self.text_len is not None else None
+        if group is not None:
+            g.check(lib.qw_gpu_group_attn_block_causal_bf16(
+                group, full, q, k, v, self.limits, w.batch, w.rows, self.heads, self.heads,
+                HEAD_DIM, tl, w.text_pad, SCALE), "group_attn_block_causal")
+            return full
         g.check(lib.qw_gpu_attn_block_causal_bf16(g.handle, out, q, k, v, self.limits, w.batch,
                                                   w.rows, self.heads, self.heads, HEAD_DIM, tl,
                                                   w.text_pad, SCALE),
