@@ -13,7 +13,9 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libqwen_attn_b200.so")
+# QWEN_METAL_B200_LIB points at another build of the library (e.g. one compiled
+# with tracing); by default the in-tree build is loaded.
+LIB_PATH = os.environ.get("QWEN_METAL_B200_LIB") or os.path.join(_HERE, "lib", "libqwen_attn_b200.so")
 
 c_gpu = C.c_void_p
 c_tensor = C.c_void_p

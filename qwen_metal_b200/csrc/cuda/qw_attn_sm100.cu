@@ -21,6 +21,12 @@
 // skipped by all roles, interior tiles run without a compare, boundary tiles
 // apply the integer compare per element.
 //
+// Epilogue: O / l is rounded to bf16 into the (by then dead) Q tile in shared
+// memory and leaves as TMA stores of the whole 128x128 tile.  When the heads
+// are sharded over several GPUs the same tile is stored into every rank's full
+// output through peer-mapped pointers, so the per-layer gather costs no extra
+// pass: the transfer is issued tile by tile while other tiles still compute.
+//
 // Every wait is bounded: when one runs out the CTA records where in the status
 // words, raises a shared abort flag that all other waits poll, drains its TMA
 // loads, frees its TMEM and returns.
@@ -630,7 +636,10 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
                 tma_store_3d(&maps_out.m[d], stage + kHalfTileBytes, col + 64, (int)tile_row0, (int)b);
             }
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            // Shared memory may be released once the stores have read it; the
+            // writes themselves are complete when the grid completes, which is
+            // what the barrier behind a sharded launch waits for.
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         }
     }
 }
