@@ -35,6 +35,11 @@ for p in (ROOT, os.path.join(ROOT, "tests")):
         sys.path.insert(0, p)
 
 NOMINAL_BF16_TFLOPS = 2250.0
+# (workload, GPUs) -> DRAM bytes one launch moved under ncu; see profiles/.
+NCU_DRAM_BYTES = {
+    (3, 1): {"attention": 194.8e6, "prologue": 172.5e6,
+             "source": "profiles/attention_sm100_cfg3.txt, profiles/prologue_cfg3.txt"},
+}
 
 
 def measured_peaks():
@@ -316,10 +321,14 @@ def run_product(args):
     flops_launch = w.flops_per_layer() / world
     attn_tflops = flops_launch / attn_s / 1e12
     prol_bytes = (2 * n_local * 2 * 2) + 2 * w.rows * 64 * 4
+    # DRAM bytes per launch from the committed ncu captures (dram__bytes_read.sum +
+    # dram__bytes_write.sum), known for the single-GPU cfg3 launch only.
+    traffic = NCU_DRAM_BYTES.get((args.workload, world), {})
     roofline = {
         "kernel": "qw_attn_sm100_kernel", "bound": "tensor", "achieved": attn_tflops,
         "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
-        "frac": attn_tflops / peaks["bf16_sustained"], "traffic": None,
+        "frac": attn_tflops / peaks["bf16_sustained"], "traffic": traffic.get("attention"),
+        "traffic_source": traffic.get("source"),
         "peak_source": f"{peaks['source']} sustained cuBLAS bf16 (kernel timed in a "
                        f"{args.steps * w.layers}-launch loop); burst {peaks['bf16']}",
         "launch_ms": attn_s * 1e3, "flops_per_launch": flops_launch,
@@ -327,7 +336,7 @@ def run_product(args):
         "prologue": {"kernel": "qw_prologue_kernel", "bound": "hbm",
                      "achieved": prol_bytes / prol_s / 1e9, "peak": peaks["hbm"], "unit": "GB/s",
                      "frac": prol_bytes / prol_s / 1e9 / peaks["hbm"], "launch_ms": prol_s * 1e3,
-                     "bytes_per_launch": prol_bytes},
+                     "bytes_per_launch": prol_bytes, "traffic": traffic.get("prologue")},
     }
 
     # ---- end to end from pinned host buffers through the C ABI (N = 1) ----
