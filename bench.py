@@ -339,6 +339,41 @@ def run_product(args):
                      "bytes_per_launch": prol_bytes, "traffic": traffic.get("prologue")},
     }
 
+    # ---- the block's element-wise neighbours of the path (single GPU only): the
+    # AdaLN norm in front of the QKV projection and the gated residual behind the
+    # output projection, on [batch*rows, heads*128] activations of this workload ----
+    if world == 1:
+        rows_all, width = w.batch * w.rows, heads_local * 128
+        rng = np.random.default_rng(7)
+        modulation = gpu.bf16(workloads.normal_bf16(rng, (2, 4, width), 0.0, 0.5))
+        row_map = gpu.u32((np.arange(rows_all) % w.rows < (w.text_pad or 0)).astype(np.uint32))
+        acts = [layers[i % len(layers)][0] for i in range(4)]  # resident q tensors as activations
+
+        def norm_only():
+            for i, x in enumerate(acts):
+                gpu.check(lib.qw_gpu_layer_norm_mod_bf16(gpu.handle, q_work, x, modulation, row_map,
+                                                         rows_all, width, 4, 0, 1e-6), "norm")
+
+        def gate_only():
+            for i, x in enumerate(acts):
+                gpu.check(lib.h3_gpu_gate_bf16(gpu.handle, q_work, x, acts[(i + 1) % 4], modulation,
+                                               row_map, rows_all, width, 4, 2), "gate")
+
+        timed(norm_only, 2), timed(gate_only, 2)
+        norm_s = timed(norm_only, 5) / 20
+        gate_s = timed(gate_only, 5) / 20
+        roofline["neighbours"] = {
+            "layer_norm_mod": {"bound": "hbm", "bytes_per_launch": 2 * n_local * 2,
+                               "achieved": 2 * n_local * 2 / norm_s / 1e9, "unit": "GB/s",
+                               "frac": 2 * n_local * 2 / norm_s / 1e9 / peaks["hbm"],
+                               "launch_ms": norm_s * 1e3},
+            "gate": {"bound": "hbm", "bytes_per_launch": 3 * n_local * 2,
+                     "achieved": 3 * n_local * 2 / gate_s / 1e9, "unit": "GB/s",
+                     "frac": 3 * n_local * 2 / gate_s / 1e9 / peaks["hbm"],
+                     "launch_ms": gate_s * 1e3},
+        }
+        gpu.free(modulation), gpu.free(row_map)
+
     # ---- end to end from pinned host buffers through the C ABI (N = 1) ----
     e2e = None
     if args.e2e and world == 1:

@@ -139,6 +139,15 @@ int h3_gpu_head_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *tensor, const h3_gpu_t
                               uint32_t sequence, uint32_t heads, uint32_t head_dim,
                               float epsilon);
 
+/* reference h3_gpu.h:406-411, h3_gpu.m:3865-3889, h3_shaders.metal:3583-3599:
+ * gated residual behind the attention / MLP branch of a DiT block,
+ * output = bf16(residual + branch * modulation[row_map[row]][gate_slot][column]);
+ * modulation is [maps][slots][width] bf16, row_map u32 per row. */
+int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                     const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
+                     const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                     uint32_t slots, uint32_t gate_slot);
+
 /* reference h3_gpu.h:537-543, h3_gpu.m:4642-4693, h3_shaders.metal:4375-4445:
  * token-causal attention; this variant folds the scale into Q and re-rounds Q
  * to bf16 before the dot products. */

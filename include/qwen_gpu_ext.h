@@ -25,6 +25,14 @@ int qw_gpu_qk_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output, h3_gpu_tensor 
                         const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
                         uint32_t sequence, uint32_t heads, uint32_t head_dim);
 
+/* reference qwen_gpu_ext.h:10-16, h3_gpu.m:5100-5124, h3_shaders.metal:4767-4813:
+ * the block's AdaLN norm in front of the QKV projection (and the MLP):
+ * affine-free LayerNorm over `width`, then (1 + modulation[row_map[row]][scale_slot]). */
+int qw_gpu_layer_norm_mod_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                               const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map,
+                               uint32_t rows, uint32_t width, uint32_t slots,
+                               uint32_t scale_slot, float epsilon);
+
 /* reference qwen_gpu_ext.h:57-60, h3_gpu.m:5258-5275, h3_shaders.metal:4975-4997:
  * per-head RMSNorm with the normalised value rounded to bf16 before the
  * weight multiply (double rounding). */

@@ -249,6 +249,49 @@ void qwo_qk_rope_bf16(uint16_t *q_out, uint16_t *k_out, const uint16_t *q_in,
             }
 }
 
+/* h3_shaders.metal:4767-4813 */
+void qwo_layer_norm_mod_bf16(uint16_t *out, const uint16_t *in,
+                             const uint16_t *modulation, const uint32_t *row_map,
+                             uint32_t rows, uint32_t width, uint32_t slots,
+                             uint32_t scale_slot, float epsilon) {
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        const uint16_t *x = in + (size_t)row * width;
+        float sum = 0.0f;
+        for (uint32_t c = 0; c < width; c++) sum += qwo_bf16_to_f32(x[c]);
+        float mean = sum / (float)width;
+        float square = 0.0f;
+        for (uint32_t c = 0; c < width; c++) {
+            float centered = qwo_bf16_to_f32(x[c]) - mean;
+            square = fmaf(centered, centered, square);
+        }
+        float inverse = 1.0f / sqrtf(square / (float)width + epsilon);
+        const uint16_t *scale =
+            modulation + ((size_t)row_map[row] * slots + scale_slot) * width;
+        for (uint32_t c = 0; c < width; c++) {
+            float normalized = (qwo_bf16_to_f32(x[c]) - mean) * inverse;
+            out[(size_t)row * width + c] =
+                qwo_f32_to_bf16(normalized * (1.0f + qwo_bf16_to_f32(scale[c])));
+        }
+    }
+}
+
+/* h3_shaders.metal:3583-3599 */
+void qwo_gate_bf16(uint16_t *out, const uint16_t *residual, const uint16_t *branch,
+                   const uint16_t *modulation, const uint32_t *row_map, uint32_t rows,
+                   uint32_t width, uint32_t slots, uint32_t gate_slot) {
+#pragma omp parallel for schedule(static)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        const uint16_t *gate =
+            modulation + ((size_t)row_map[row] * slots + gate_slot) * width;
+        for (uint32_t c = 0; c < width; c++) {
+            size_t index = (size_t)row * width + c;
+            float product = qwo_bf16_to_f32(branch[index]) * qwo_bf16_to_f32(gate[c]);
+            out[index] = qwo_f32_to_bf16(qwo_bf16_to_f32(residual[index]) + product);
+        }
+    }
+}
+
 /* tests/test_prefix_kernel.c:72-97, one (batch,row): all heads. */
 static uint64_t sdpa_row(float *out, const uint16_t *q, const uint16_t *k,
                          const uint16_t *v, uint32_t b, uint32_t r, uint32_t limit,

@@ -114,6 +114,23 @@ uint64_t qwo_visible_pairs(const uint32_t *kv_limit, int per_batch_limits,
                            uint32_t batch, uint32_t q_rows, uint32_t kv_rows,
                            const uint32_t *text_len, uint32_t text_pad);
 
+/* Affine-free LayerNorm over `width` bf16 values per row, then the per-row
+ * modulation scale: out = bf16((x - mean) * rsqrt(var + eps) * (1 + scale)),
+ * scale = modulation[row_map[row]][scale_slot][column], two-pass variance with
+ * an fma sum of squares, all fp32 (h3_shaders.metal:4767-4813; the shader's
+ * 256-way tree sum is restated as a serial sum). */
+void qwo_layer_norm_mod_bf16(uint16_t *out, const uint16_t *in,
+                             const uint16_t *modulation, const uint32_t *row_map,
+                             uint32_t rows, uint32_t width, uint32_t slots,
+                             uint32_t scale_slot, float epsilon);
+
+/* out = bf16(residual + branch * gate), gate =
+ * modulation[row_map[row]][gate_slot][column], fp32, unfused product and sum
+ * (h3_shaders.metal:3583-3599). */
+void qwo_gate_bf16(uint16_t *out, const uint16_t *residual, const uint16_t *branch,
+                   const uint16_t *modulation, const uint32_t *row_map, uint32_t rows,
+                   uint32_t width, uint32_t slots, uint32_t gate_slot);
+
 int qwo_threads(void);
 
 #ifdef __cplusplus

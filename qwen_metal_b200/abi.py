@@ -78,6 +78,8 @@ _SIGNATURES = {
     "h3_gpu_sdpa_bf16_head_major_output": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, f32]),
     "h3_gpu_head_rms_norm_bf16": (C.c_int, [c_gpu, c_tensor, c_tensor, u32, u32, u32, f32]),
+    "h3_gpu_gate_bf16": (
+        C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32]),
     "h3_gpu_gqa_causal_bf16": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32, f32]),
     "h3_gpu_gqa_causal_noalloc_bf16": (
@@ -85,6 +87,8 @@ _SIGNATURES = {
     "qw_gpu_qk_rope_bf16": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32]),
     "qw_gpu_head_rms_norm_bf16": (C.c_int, [c_gpu, c_tensor, c_tensor, u32, u32, u32, f32]),
+    "qw_gpu_layer_norm_mod_bf16": (
+        C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32, f32]),
     "qw_gpu_flash_sdpa_bf16": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32, f32]),
     "qw_gpu_flash_sdpa_prefix_bf16": (

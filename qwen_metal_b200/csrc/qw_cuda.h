@@ -99,6 +99,26 @@ typedef struct {
 
 int qwcu_prologue_launch(const qwcu_prologue_args *args, qwcu_stream stream);
 
+/* The element-wise neighbours of the attention path: rows of `width` bf16
+ * values, a modulation tensor [maps][slots][width] and a per-row map index.
+ *   layer_norm_mod: output = LayerNorm(input) * (1 + modulation[map][slot])
+ *   gate          : output = input + branch * modulation[map][slot] */
+typedef struct {
+    const void *input;  /* norm input / gate residual */
+    const void *branch; /* gate only */
+    const void *modulation;
+    const uint32_t *row_map;
+    void *output;
+    uint32_t rows;
+    uint32_t width;
+    uint32_t slots;
+    uint32_t slot;
+    float epsilon; /* norm only */
+} qwcu_rowwise_args;
+
+int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *args, qwcu_stream stream);
+int qwcu_gate_launch(const qwcu_rowwise_args *args, int sm_count, qwcu_stream stream);
+
 /* h3 causal variant helper: out = bf16(in * scale), elementwise. */
 int qwcu_scale_bf16_launch(void *out, const void *in, size_t elements, float scale,
                            qwcu_stream stream);

@@ -57,6 +57,63 @@ int qw_gpu_head_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *tensor, const h3_gpu_t
     return head_norm(gpu, tensor, weight, sequence, heads, head_dim, epsilon, 1);
 }
 
+/* reference h3_gpu.m:5100-5124 */
+int qw_gpu_layer_norm_mod_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                               const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map,
+                               uint32_t rows, uint32_t width, uint32_t slots,
+                               uint32_t scale_slot, float epsilon) {
+    if (!gpu) return 0;
+    size_t count = (size_t)rows * width;
+    if (!qw_require_dtype(gpu, input, count, H3_GPU_BF16, "Qwen AdaLN input") ||
+        !qw_require_dtype(gpu, modulation, 1, H3_GPU_BF16, "Qwen AdaLN modulation") ||
+        !qw_require_dtype(gpu, row_map, rows, H3_GPU_U32, "Qwen AdaLN row map") ||
+        !qw_require_dtype(gpu, output, count, H3_GPU_BF16, "Qwen AdaLN output"))
+        return 0;
+    if (scale_slot >= slots) {
+        qw_set_error(gpu, "Qwen AdaLN: scale slot %u outside %u slots", scale_slot, slots);
+        return 0;
+    }
+    if (!rows || !width) {
+        qw_set_error(gpu, "Qwen AdaLN: empty geometry");
+        return 0;
+    }
+    if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
+    qwcu_rowwise_args args = {input->dev, NULL, modulation->dev, row_map->dev, output->dev,
+                              rows, width, slots, scale_slot, epsilon};
+    int rc = qwcu_layer_norm_mod_launch(&args, gpu->stream);
+    qw_count_launch(gpu, rc, "Qwen AdaLN");
+    return rc == 0;
+}
+
+/* reference h3_gpu.m:3865-3889 */
+int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                     const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
+                     const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                     uint32_t slots, uint32_t gate_slot) {
+    if (!gpu) return 0;
+    size_t count = (size_t)rows * width;
+    if (!qw_require_dtype(gpu, residual, count, H3_GPU_BF16, "gate residual") ||
+        !qw_require_dtype(gpu, branch, count, H3_GPU_BF16, "gate branch") ||
+        !qw_require_dtype(gpu, modulation, 1, H3_GPU_BF16, "gate modulation") ||
+        !qw_require_dtype(gpu, row_map, rows, H3_GPU_U32, "gate row map") ||
+        !qw_require_dtype(gpu, output, count, H3_GPU_BF16, "gate output"))
+        return 0;
+    if (gate_slot >= slots) {
+        qw_set_error(gpu, "gate: slot %u outside %u slots", gate_slot, slots);
+        return 0;
+    }
+    if (!rows || !width) {
+        qw_set_error(gpu, "gate: empty geometry");
+        return 0;
+    }
+    if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
+    qwcu_rowwise_args args = {residual->dev, branch->dev, modulation->dev, row_map->dev,
+                              output->dev, rows, width, slots, gate_slot, 0.0f};
+    int rc = qwcu_gate_launch(&args, qwcu_device_sm_count(gpu->device), gpu->stream);
+    qw_count_launch(gpu, rc, "gate");
+    return rc == 0;
+}
+
 /* reference h3_gpu.m:5159-5193 */
 int qw_gpu_qk_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output, h3_gpu_tensor *key_output,
                         const h3_gpu_tensor *query_input, const h3_gpu_tensor *key_input,

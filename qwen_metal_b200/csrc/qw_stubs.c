@@ -50,7 +50,6 @@ QW_STUB_OP(h3_gpu_embedding_bf16)
 QW_STUB_OP(h3_gpu_euler_bf16)
 QW_STUB_OP(h3_gpu_gate_adaln_bf16)
 QW_STUB_OP(h3_gpu_gate_adaln_quantize_int8)
-QW_STUB_OP(h3_gpu_gate_bf16)
 QW_STUB_OP(h3_gpu_gate_f32)
 QW_STUB_OP(h3_gpu_geglu_f32)
 QW_STUB_OP(h3_gpu_gelu_bf16)
@@ -99,7 +98,6 @@ QW_STUB_OP(h3_gpu_vae_encoder_pad_f32)
 QW_STUB_OP(h3_gpu_video_qkv_rope_f32)
 QW_STUB_OP(h3_gpu_vision_qkv_rope_bf16)
 QW_STUB_OP(h3_gpu_weight_norm_f32)
-QW_STUB_OP(qw_gpu_layer_norm_mod_bf16)
 QW_STUB_OP(qw_gpu_qk_rope_half_bf16)
 QW_STUB_OP(qw_gpu_qkv_bf16)
 QW_STUB_OP(qw_gpu_rms_norm_bf16)

@@ -15,6 +15,11 @@ It writes only small data files next to this script:
   host_ref_rope.json       the 144 released-table samples of tests/host_ref.h:19-57
   dit_segments.json        run layout of fixture case c (tests/dit_fixture/meta.json)
   reference_abi_names.json the function names declared by h3_gpu.h and qwen_gpu_ext.h
+  ref_block_stages.npz     stage tensors of the reference's DiT block fixture
+                           (tests/dit_fixture/{a,b}_*.bin, bf16 [rows, 4096]; the stages
+                           tests/test_dit_block.c:204-212 compares) around the AdaLN norm
+                           and the gated residual: joint_in, modulation [2,4,4096], attn_in
+                           for cases a and b; attn_out, mlp_in, mlp_out, block_out for b
   kat_prefix_sdpa.json     verdict of the reference's tests/test_prefix_kernel.c
                            compiled unmodified with the CPU oracle behind the op
                            (oracle/_ref/test_prefix_kernel_oracle), plus a checksum of
@@ -78,6 +83,17 @@ def main():
                "heads": meta["heads"], "head_dim": meta["head_dim"], "eps": meta["eps"],
                "cases": meta["cases"]},
               open(os.path.join(HERE, "dit_segments.json"), "w"))
+
+    stages = {}
+    for case, names in (("a", ("joint_in", "modulation", "attn_in")),
+                        ("b", ("joint_in", "modulation", "attn_in", "attn_out", "mlp_in",
+                               "mlp_out", "block_out"))):
+        for name in names:
+            data = np.fromfile(os.path.join(ref, "tests/dit_fixture", f"{case}_{name}.bin"),
+                               dtype="<u2")
+            stages[f"{case}_{name}"] = data.reshape(-1, meta["hidden"])
+        stages[f"{case}_text_rows"] = np.array(meta["cases"][case]["text_rows"], np.uint32)
+    np.savez_compressed(os.path.join(HERE, "ref_block_stages.npz"), **stages)
 
     # every function name the two ABI headers declare (names only)
     abi_names = set()

@@ -21,6 +21,11 @@ class Segment(C.Structure):
 _lib = None
 
 
+def bf16_to_f32(bits):
+    """bf16 bit patterns (uint16) as float32 values."""
+    return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
 def _p(a):
     return None if a is None else a.ctypes.data_as(C.c_void_p)
 
@@ -53,6 +58,10 @@ def load():
         lib.qwo_qk_rope_bf16.restype = None
         lib.qwo_qk_rope_bf16.argtypes = [C.c_void_p] * 6 + [C.c_uint32] * 3
         lib.qwo_kat_fill.restype = None
+        lib.qwo_layer_norm_mod_bf16.argtypes = [C.c_void_p] * 4 + [C.c_uint32] * 4 + [C.c_float]
+        lib.qwo_layer_norm_mod_bf16.restype = None
+        lib.qwo_gate_bf16.argtypes = [C.c_void_p] * 5 + [C.c_uint32] * 4
+        lib.qwo_gate_bf16.restype = None
         lib.qwo_kat_fill.argtypes = [C.c_uint32] + [C.c_void_p] * 3 + [C.c_size_t]
         lib.qwo_kat_limits.restype = None
         lib.qwo_kat_limits.argtypes = [C.c_void_p]
@@ -131,6 +140,27 @@ def head_rms_norm(x, weight, sequence, heads, eps, double_round=False):
     lib.qwo_head_rms_norm_bf16(_p(out), _p(np.ascontiguousarray(weight, dtype=np.uint16)),
                                sequence, heads, 128, eps, int(double_round))
     return out
+
+
+def layer_norm_mod(x, modulation, row_map, rows, width, slots, scale_slot, eps):
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    modulation = np.ascontiguousarray(modulation, dtype=np.uint16)
+    row_map = np.ascontiguousarray(row_map, dtype=np.uint32)
+    out = np.empty(rows * width, np.uint16)
+    load().qwo_layer_norm_mod_bf16(_p(out), _p(x), _p(modulation), _p(row_map), rows, width,
+                                   slots, scale_slot, eps)
+    return out.reshape(rows, width)
+
+
+def gate(residual, branch, modulation, row_map, rows, width, slots, gate_slot):
+    residual = np.ascontiguousarray(residual, dtype=np.uint16)
+    branch = np.ascontiguousarray(branch, dtype=np.uint16)
+    modulation = np.ascontiguousarray(modulation, dtype=np.uint16)
+    row_map = np.ascontiguousarray(row_map, dtype=np.uint32)
+    out = np.empty(rows * width, np.uint16)
+    load().qwo_gate_bf16(_p(out), _p(residual), _p(branch), _p(modulation), _p(row_map), rows,
+                         width, slots, gate_slot)
+    return out.reshape(rows, width)
 
 
 def qk_rope(q, k, cos, sin, sequence, heads):
