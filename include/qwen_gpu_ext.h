@@ -97,6 +97,24 @@ int qw_gpu_qk_norm_rope_out_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
                                  uint32_t batch, uint32_t sequence, uint32_t heads,
                                  uint32_t head_dim, float epsilon);
 
+/* NEW: the prologue of a target-only layer of the edit path, where only the
+ * target image rows are recomputed against the per-layer K/V cache of an
+ * earlier full pass (reference qwen_dit.m:1872-1904 runs two head norms, the
+ * rotation and two h3_gpu_copy_bf16 scatters for this).  query [rows, heads,
+ * 128] is normed and rotated in place; key_new is normed, rotated and written to
+ * rows [cache_row_offset, cache_row_offset + rows) of key_cache [cache_rows,
+ * heads, 128]; value_new is copied to the same rows of value_cache.  The tables
+ * are the target rows' slices, [rows, 64] f32.  Follow it with
+ * qw_gpu_sdpa_rect_bf16(out, query, key_cache, value_cache, rows, cache_rows, ...). */
+int qw_gpu_qk_norm_rope_cache_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key_cache,
+                                   h3_gpu_tensor *value_cache, const h3_gpu_tensor *key_new,
+                                   const h3_gpu_tensor *value_new,
+                                   const h3_gpu_tensor *norm_weight_q,
+                                   const h3_gpu_tensor *norm_weight_k,
+                                   const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                   uint32_t cache_rows, uint32_t cache_row_offset, uint32_t rows,
+                                   uint32_t heads, uint32_t head_dim, float epsilon);
+
 /* Batched block-causal attention with optional key padding (classifier-free
  * guidance runs cond/uncond as batch items whose text lengths differ).
  *   q, out [batch, rows, heads, 128]; k, v [batch, rows, kv_heads, 128]

@@ -45,6 +45,8 @@ struct Params {
     const uint4 *k_in;
     uint4 *q_out;
     uint4 *k_out;
+    const uint4 *v_in;  // optional third tensor: copied as is (K/V cache update)
+    uint4 *v_out;
     const uint4 *wq;
     const uint4 *wk;
     const float4 *cos_t;
@@ -71,26 +73,32 @@ constexpr int kHeadsPerTrip = 4;
 // A half-warp owns one (row, tensor) strip: it keeps its 8-element slice of the
 // norm weight and of the row's cos/sin in registers and walks the heads, four at
 // a time.  Lane l holds elements [8l, 8l+8) of every head = RoPE pairs 4l..4l+3.
+// The two half-warps of a warp may hold different tensors (a normed key strip
+// next to a copied value strip), so the reductions name their own 16 lanes.
 __global__ void __launch_bounds__(256) qw_prologue_kernel(const Params p) {
     const int lane16 = threadIdx.x & 15;
+    const uint32_t half_mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
     const uint32_t half_warps = (gridDim.x * blockDim.x) >> 4;
     // Both half-warps of a warp run the same number of trips (the strip count is
     // padded to an even number by the host): the shuffles need the whole warp.
     for (uint32_t strip = (blockIdx.x * blockDim.x + threadIdx.x) >> 4; strip < p.strips;
          strip += half_warps) {
         const uint32_t row = strip / (uint32_t)p.tensors;
-        const bool is_k = (strip % (uint32_t)p.tensors) != 0;
+        const uint32_t which = strip - row * (uint32_t)p.tensors;  // 0 query, 1 key, 2 value
         const bool live = row < p.rows;
-        const uint4 *src = (is_k ? p.k_in : p.q_in) + (size_t)row * p.heads * 16 + lane16;
-        uint4 *dst = (is_k ? p.k_out : p.q_out) + (size_t)row * p.heads * 16 + lane16;
-        const uint4 *w = is_k ? p.wk : p.wq;
+        const uint4 *src = (which == 0 ? p.q_in : which == 1 ? p.k_in : p.v_in) +
+                           (size_t)row * p.heads * 16 + lane16;
+        uint4 *dst = (which == 0 ? p.q_out : which == 1 ? p.k_out : p.v_out) +
+                     (size_t)row * p.heads * 16 + lane16;
+        const uint4 *w = which == 0 ? p.wq : which == 1 ? p.wk : nullptr;
+        const bool rotate = p.cos_t && which < 2;
         float wf[8], cc[4], sn[4];
         if (w) {
             const uint4 wv = w[lane16];
             wf[0] = bf16_lo(wv.x); wf[1] = bf16_hi(wv.x); wf[2] = bf16_lo(wv.y); wf[3] = bf16_hi(wv.y);
             wf[4] = bf16_lo(wv.z); wf[5] = bf16_hi(wv.z); wf[6] = bf16_lo(wv.w); wf[7] = bf16_hi(wv.w);
         }
-        if (p.cos_t) {
+        if (rotate) {
             const size_t t = (size_t)((live ? row : 0u) % p.table_rows) * 16 + lane16;
             const float4 c = p.cos_t[t], s4 = p.sin_t[t];
             cc[0] = c.x; cc[1] = c.y; cc[2] = c.z; cc[3] = c.w;
@@ -113,7 +121,7 @@ __global__ void __launch_bounds__(256) qw_prologue_kernel(const Params p) {
                     for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
 #pragma unroll
                     for (int off = 8; off > 0; off >>= 1)
-                        ss += __shfl_xor_sync(0xffffffffu, ss, off, 16);
+                        ss += __shfl_xor_sync(half_mask, ss, off, 16);
                     // mean = ss / 128 exactly; 1/sqrt to within 2 ulp of the reference's rsqrt
                     const float inv = rsqrtf(__fadd_rn(ss * 0.0078125f, p.eps));
 #pragma unroll
@@ -126,7 +134,7 @@ __global__ void __launch_bounds__(256) qw_prologue_kernel(const Params p) {
                         }
                         y[i >> 1] = pack_bf16x2(__fmul_rn(n0, wf[i]), __fmul_rn(n1, wf[i + 1]));
                     }
-                    if (p.cos_t) {
+                    if (rotate) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {  // the bf16 store between norm and rotation
                             v[2 * i] = bf16_lo(y[i]);
@@ -134,7 +142,7 @@ __global__ void __launch_bounds__(256) qw_prologue_kernel(const Params p) {
                         }
                     }
                 }
-                if (p.cos_t) {
+                if (rotate) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float e = v[2 * i], o = v[2 * i + 1];
@@ -189,7 +197,10 @@ extern "C" int qwcu_prologue_launch(const qwcu_prologue_args *a, qwcu_stream str
     p.heads = a->heads;
     p.eps = a->epsilon;
     p.double_round = a->double_round;
-    p.tensors = a->k_in ? 2 : 1;
+    p.v_in = static_cast<const uint4 *>(a->v_in);
+    p.v_out = static_cast<uint4 *>(a->v_out);
+    if (a->v_in && (!a->k_in || !a->v_out)) return (int)cudaErrorInvalidValue;
+    p.tensors = a->v_in ? 3 : a->k_in ? 2 : 1;
     unsigned long long strips = (unsigned long long)a->rows * p.tensors;
     strips = (strips + 1ull) & ~1ull;  // whole warps iterate together
     if (strips > 0xffffffffull) return (int)cudaErrorInvalidValue;

@@ -80,12 +80,16 @@ int qwcu_attn_scalar_launch(const qwcu_attn_args *args, qwcu_stream stream);
  *   norm_weight_q/k == NULL -> no norm for that tensor
  *   rope_cos == NULL        -> no rotation
  *   k_in == NULL            -> only q is processed
+ *   v_in != NULL            -> a third tensor of the same shape is copied to
+ *                              v_out untouched (K/V cache update in one launch)
  * double_round selects bf16(bf16(x*inv)*w). */
 typedef struct {
     const void *q_in;
     const void *k_in;
     void *q_out;
     void *k_out;
+    const void *v_in;
+    void *v_out;
     const void *norm_weight_q;
     const void *norm_weight_k;
     const float *rope_cos;

@@ -206,6 +206,67 @@ int qw_gpu_qk_norm_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *k
                                         heads, head_dim, epsilon);
 }
 
+/* The target-only layer of the edit path (reference qwen_dit.m:1872-1904): the new
+ * target rows' q is normed and rotated in place, their k is normed, rotated and
+ * written straight into rows [cache_row_offset, +rows) of the layer's key cache,
+ * and their v is copied into the same rows of the value cache -- one launch for
+ * the reference's two norms, the rotation and the two scatter copies. */
+int qw_gpu_qk_norm_rope_cache_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key_cache,
+                                   h3_gpu_tensor *value_cache, const h3_gpu_tensor *key_new,
+                                   const h3_gpu_tensor *value_new,
+                                   const h3_gpu_tensor *norm_weight_q,
+                                   const h3_gpu_tensor *norm_weight_k,
+                                   const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                   uint32_t cache_rows, uint32_t cache_row_offset, uint32_t rows,
+                                   uint32_t heads, uint32_t head_dim, float epsilon) {
+    if (!gpu) return 0;
+    size_t count = (size_t)rows * heads * head_dim;
+    size_t cache_count = (size_t)cache_rows * heads * head_dim;
+    size_t rope_count = (size_t)rows * (head_dim / 2);
+    if (!qw_require_dtype(gpu, query, count, H3_GPU_BF16, "QK norm+rope cache query") ||
+        !qw_require_dtype(gpu, key_new, count, H3_GPU_BF16, "QK norm+rope cache key") ||
+        !qw_require_dtype(gpu, value_new, count, H3_GPU_BF16, "QK norm+rope cache value") ||
+        !qw_require_dtype(gpu, key_cache, cache_count, H3_GPU_BF16, "QK norm+rope key cache") ||
+        !qw_require_dtype(gpu, value_cache, cache_count, H3_GPU_BF16, "QK norm+rope value cache") ||
+        !qw_require_dtype(gpu, norm_weight_q, head_dim, H3_GPU_BF16, "QK norm+rope cache query weight") ||
+        !qw_require_dtype(gpu, norm_weight_k, head_dim, H3_GPU_BF16, "QK norm+rope cache key weight") ||
+        !qw_require_dtype(gpu, rope_cos, rope_count, H3_GPU_F32, "QK norm+rope cache cosine") ||
+        !qw_require_dtype(gpu, rope_sin, rope_count, H3_GPU_F32, "QK norm+rope cache sine"))
+        return 0;
+    if (!qw_require_command(gpu)) return 0;
+    if (head_dim != 128 || !rows || !heads) {
+        qw_set_error(gpu, "QK norm+rope cache: unsupported geometry");
+        return 0;
+    }
+    if ((uint64_t)cache_row_offset + rows > cache_rows) {
+        qw_set_error(gpu, "QK norm+rope cache: rows [%u, %u) lie outside the %u cached rows",
+                     cache_row_offset, cache_row_offset + rows, cache_rows);
+        return 0;
+    }
+    if (key_new == key_cache || value_new == value_cache) {
+        qw_set_error(gpu, "QK norm+rope cache: the new rows and the cache must be distinct tensors");
+        return 0;
+    }
+    size_t offset_bytes = (size_t)cache_row_offset * heads * head_dim * 2;
+    qwcu_prologue_args args;
+    memset(&args, 0, sizeof(args));
+    args.q_in = query->dev;
+    args.q_out = query->dev;
+    args.k_in = key_new->dev;
+    args.k_out = (char *)key_cache->dev + offset_bytes;
+    args.v_in = value_new->dev;
+    args.v_out = (char *)value_cache->dev + offset_bytes;
+    args.norm_weight_q = norm_weight_q->dev;
+    args.norm_weight_k = norm_weight_k->dev;
+    args.rope_cos = rope_cos->dev;
+    args.rope_sin = rope_sin->dev;
+    args.rows = rows;
+    args.table_rows = rows;
+    args.heads = heads;
+    args.epsilon = epsilon;
+    return launch_prologue(gpu, &args, "QK norm+rope cache");
+}
+
 /* ---- attention ops ------------------------------------------------------- */
 
 int qw_launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what) {

@@ -7,6 +7,7 @@ Gates on bf16 outputs (stated once here, used everywhere):
 Integer work (limits, mask indexing) is checked bit-exactly.
 """
 import ctypes as C
+import dataclasses
 import math
 import os
 import subprocess
@@ -465,3 +466,73 @@ def test_rope_tables_on_device_match_host(gpu):
     lib.h3_gpu_tensor_free(cos_t), lib.h3_gpu_tensor_free(sin_t)
     assert lib.qw_pipe_rope_tables(gpu.handle, 0, 8, 8, C.byref(cos_t), C.byref(sin_t), err, 256) == 0
     assert b"bad arguments" in err.value
+
+
+# --------------------------------------------------------------------------
+# edit path after the first step: target rows only, against the K/V cache
+# --------------------------------------------------------------------------
+def test_target_only_layer_matches_full_layer(gpu):
+    """Reference qwen_dit.m:1694-1710, 1872-1904: a full pass leaves every layer's
+    K/V in a cache; later steps recompute only the target image rows.  One layer of
+    that: the cache holds the full pass's normed + rotated K and V; the target
+    rows' fresh q/k/v go through qw_gpu_qk_norm_rope_cache_bf16 (k, v land in the
+    cache rows) and qw_gpu_sdpa_rect_bf16.  With unchanged inputs the result must
+    equal the full layer's target rows bit for bit (same per-row arithmetic), the
+    cache must be unchanged outside the target rows, and both must match the oracle."""
+    w = workloads.workload(4)
+    w = dataclasses.replace(w, heads=4)          # text 256 + condition 4096 + target 4096
+    rows, H = w.rows, w.heads
+    t_rows = w.runs[-1][0]
+    t_base = rows - t_rows
+    q, k, v, wq, wk = workloads.layer_inputs(w, 0)
+    cos, sin = w.rope_tables()
+    lib = gpu.lib
+    # full pass of the layer: prologue in place, prefix attention
+    qt, kt, vt, wqt, wkt = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.bf16(wq), gpu.bf16(wk)
+    ct, st, lt = gpu.f32(cos), gpu.f32(sin), gpu.u32(w.limits())
+    full = gpu.new_bf16(q.size)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_qk_norm_rope_bf16(gpu.handle, qt, kt, wqt, wkt, ct, st, 1, rows, H, 128,
+                                           workloads.EPS), "prologue")
+    gpu.check(lib.qw_gpu_flash_sdpa_prefix_bf16(gpu.handle, full, qt, kt, vt, lt, rows, rows, H, H,
+                                                128, SCALE), "prefix attention")
+    gpu.submit()
+    full_out = gpu.read_bf16(full, q.size).reshape(rows, H, 128)
+    k_cache_ref = gpu.read_bf16(kt, k.size).reshape(rows, H, 128)
+    # target-only step: poison the target rows of the cache, then refill them
+    k_cache = k_cache_ref.copy()
+    v_cache = v.reshape(rows, H, 128).copy()
+    k_cache[t_base:] = 0x7FC0
+    v_cache[t_base:] = 0x7FC0
+    kc, vc = gpu.bf16(k_cache), gpu.bf16(v_cache)
+    tq = gpu.bf16(q.reshape(rows, H, 128)[t_base:])
+    tk = gpu.bf16(k.reshape(rows, H, 128)[t_base:])
+    tv = gpu.bf16(v.reshape(rows, H, 128)[t_base:])
+    tc, ts = gpu.f32(cos[t_base:]), gpu.f32(sin[t_base:])
+    out = gpu.new_bf16(t_rows * H * 128)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_qk_norm_rope_cache_bf16(gpu.handle, tq, kc, vc, tk, tv, wqt, wkt, tc, ts,
+                                                 rows, t_base, t_rows, H, 128, workloads.EPS),
+              "cache prologue")
+    gpu.check(lib.qw_gpu_sdpa_rect_bf16(gpu.handle, out, tq, kc, vc, t_rows, rows, H, 128, SCALE),
+              "rect attention")
+    gpu.submit()
+    got = gpu.read_bf16(out, t_rows * H * 128).reshape(t_rows, H, 128)
+    assert np.array_equal(gpu.read_bf16(kc, k.size).reshape(rows, H, 128), k_cache_ref)
+    assert np.array_equal(gpu.read_bf16(vc, v.size).reshape(rows, H, 128), v.reshape(rows, H, 128))
+    assert np.array_equal(got, full_out[t_base:])
+    # and against the oracle on a sample of target rows
+    qo, ko = prologue_oracle(q, k, wq, wk, cos, sin, 1, rows, H)
+    sample = np.unique(np.concatenate([np.arange(0, 8), np.arange(t_rows - 8, t_rows),
+                                       np.random.default_rng(5).integers(0, t_rows, 48)]))
+    ref, _ = O.sdpa(qo.reshape(rows, H, 128)[t_base:], ko, v, None, 1, t_rows, rows, H, H, SCALE,
+                    None, 0, sample)
+    gates(got[sample], ref.reshape(t_rows, H, 128)[sample], "target-only layer vs oracle")
+    # the error convention: rows outside the cache
+    gpu.begin()
+    assert not lib.qw_gpu_qk_norm_rope_cache_bf16(gpu.handle, tq, kc, vc, tk, tv, wqt, wkt, tc, ts,
+                                                  rows, t_base + 1, t_rows, H, 128, workloads.EPS)
+    assert "outside" in gpu.error()
+    gpu.submit()
+    for t in (qt, kt, vt, wqt, wkt, ct, st, lt, full, kc, vc, tq, tk, tv, tc, ts, out):
+        gpu.free(t)
