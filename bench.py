@@ -225,7 +225,7 @@ def run_product(args):
         q, k, v, wq, wk = workloads.layer_inputs(w, layer)
         sl = [np.ascontiguousarray(x[:, :, h0:h0 + heads_local]) for x in (q, k, v)]
         layers.append(tuple(gpu.bf16(x) for x in sl) + (gpu.bf16(wq), gpu.bf16(wk)))
-        if args.e2e and world == 1 and layer < args.e2e_layers:
+        if args.e2e and layer < args.e2e_layers:
             host_layers.append(sl)
     q_work, k_work = gpu.new_bf16(n_local), gpu.new_bf16(n_local)
     out_local = gpu.new_bf16(n_local)
@@ -376,8 +376,9 @@ def run_product(args):
 
     # ---- end to end from pinned host buffers through the C ABI (N = 1) ----
     e2e = None
-    if args.e2e and world == 1:
-        e2e = run_e2e(args, gpu, w, runner, host_layers, layers, q_work, k_work, out_local)
+    if args.e2e and (world == 1 or fused):
+        e2e = run_e2e(args, gpu, w, runner, host_layers, layers, out_local,
+                      group if fused else None, out_full, world, barrier)
 
     cpu = None
     if rank == 0 and not args.no_cpu:
@@ -418,13 +419,18 @@ def run_product(args):
         dist.destroy_process_group()
 
 
-def run_e2e(args, gpu, w, runner, host_layers, layers, q_work, k_work, out_local):
+def run_e2e(args, gpu, w, runner, host_layers, layers, out_local, group, out_full, world, barrier):
     """Same metric through the C-ABI calls a host program makes: every layer's
-    q, k, v start in pinned HOST memory (h3_gpu_tensor_write_bf16), the ops run,
-    and the layer's output is read back to pinned host memory."""
+    q, k, v (this rank's heads) start in pinned HOST memory
+    (h3_gpu_tensor_write_bf16), the ops run, and the layer's output -- the full
+    gathered [rows, H*128] on every rank when the heads are sharded -- is read
+    back to pinned host memory.  Host wall clock, max over ranks."""
     import ctypes as C
+    import torch
+    import torch.distributed as dist
     lib = gpu.lib
     n = runner.n
+    n_out = n * world if group else n
     nl = len(host_layers)
     pinned = []
     for sl in host_layers:
@@ -436,7 +442,7 @@ def run_e2e(args, gpu, w, runner, host_layers, layers, q_work, k_work, out_local
             C.memmove(p, x.ctypes.data, n * 2)
             bufs.append(p)
         pinned.append(bufs)
-    out_host = lib.qw_gpu_host_alloc(n * 2)
+    out_host = lib.qw_gpu_host_alloc(n_out * 2)
     dq, dk, dv = gpu.new_bf16(n), gpu.new_bf16(n), gpu.new_bf16(n)
 
     def step():
@@ -446,32 +452,46 @@ def run_e2e(args, gpu, w, runner, host_layers, layers, q_work, k_work, out_local
             lib.h3_gpu_tensor_write_bf16(dk, hk, n)
             lib.h3_gpu_tensor_write_bf16(dv, hv, n)
             _, _, _, wqt, wkt = layers[i]
-            runner.enqueue(dq, dk, dv, wqt, wkt, out=out_local)
-            gpu.check(lib.qw_gpu_tensor_read_async(gpu.handle, out_local, out_host, n), "read")
+            if group:
+                full = out_full[i & 1]
+                runner.enqueue(dq, dk, dv, wqt, wkt, group=group, full=full)
+                gpu.check(lib.qw_gpu_group_wait_output(group, full), "wait_output")
+                gpu.check(lib.qw_gpu_tensor_read_async(gpu.handle, full, out_host, n_out), "read")
+            else:
+                runner.enqueue(dq, dk, dv, wqt, wkt, out=out_local)
+                gpu.check(lib.qw_gpu_tensor_read_async(gpu.handle, out_local, out_host, n), "read")
 
-    import torch
     steps = max(1, min(args.steps, 5))
     gpu.begin(); step(); gpu.submit()
-    torch.cuda.synchronize()
+    barrier()
     before = gpu.stats().gpu_seconds
     t0 = time.perf_counter()
     gpu.begin()
     for _ in range(steps):
         step()
     gpu.submit()
+    barrier()
     wall = time.perf_counter() - t0
     device_s = gpu.stats().gpu_seconds - before
+    if world > 1:
+        t = torch.tensor([wall, device_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        wall, device_s = float(t[0].item()), float(t[1].item())
     for bufs in pinned:
         for p in bufs:
             lib.qw_gpu_host_free(p)
     lib.qw_gpu_host_free(out_host)
+    for t in (dq, dk, dv):
+        gpu.free(t)
     flops = w.flops_per_layer() * w.layers * steps
     return {"value": flops / wall / 1e12, "unit": "TFLOP/s",
-            "h2d_bytes_per_step": 3 * n * 2 * w.layers, "d2h_bytes_per_step": n * 2 * w.layers,
+            "h2d_bytes_per_step": 3 * n * 2 * w.layers * world,
+            "d2h_bytes_per_step": n_out * 2 * w.layers * world,
             "ms_per_step": wall / steps * 1e3, "device_ms_per_step": device_s / steps * 1e3,
             "steps": steps,
-            "note": f"host wall clock around {steps} steps incl. submit; {nl} distinct pinned "
-                    "layer input sets cycled over the 32 layers"}
+            "note": f"host wall clock around {steps} steps incl. submit, max over ranks; byte "
+                    f"counts summed over the {world} rank(s); {nl} distinct pinned layer input "
+                    "sets cycled over the 32 layers"}
 
 
 def main():
