@@ -52,47 +52,65 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples during the timed region (read only)."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi clock / throttle-reason samples while the GPU runs the timed work
+    (read only).  The sampler is started early and the samples are filtered by the
+    host-clock windows in which timed work was in flight, so that a timed region
+    shorter than the sampling period still gets its samples."""
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device):
         self.device, self.proc, self.path = device, None, f"/tmp/qw_clocks_{os.getpid()}.csv"
+        self.windows = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.device)],
+                 "-lms", "50", "-i", str(self.device)],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+            return
+        deadline = time.time() + 3.0  # first sample = the tool is up
+        while time.time() < deadline and os.path.getsize(self.path) == 0:
+            time.sleep(0.02)
+
+    def window(self, t0, t1):
+        self.windows.append((t0, t1))
 
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         self.proc.wait()
-        sm, mx, reasons = [], [], set()
+        import datetime
+        inside, nearby = [], []
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in open(self.path):
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                sample = (float(parts[2]), float(parts[3]),
+                          [n for n, flag in zip(names, parts[6:10]) if flag.lower().startswith("active")])
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
+            if any(t0 - 0.01 <= stamp <= t1 + 0.01 for t0, t1 in self.windows):
+                inside.append(sample)
+            elif any(t0 - 0.01 <= stamp <= t1 + 0.12 for t0, t1 in self.windows):
+                nearby.append(sample)
         os.unlink(self.path)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+        used = inside or nearby
+        reasons = sorted({r for s_ in used for r in s_[2]})
+        return {"sm_mhz": statistics.median([s_[0] for s_ in used]) if used else None,
+                "sm_max_mhz": max(s_[1] for s_ in used) if used else None,
+                "samples": len(used), "reasons": reasons,
+                "sampled": "during the timed step and the per-kernel loops" if inside else
+                           "within 0.12 s after the timed work (none fell inside it)"}
 
 
 def oracle_prologue(O, w, q, k, wq, wk, cos, sin):
@@ -293,9 +311,10 @@ def run_product(args):
     if rank == 0:
         sampler.start()
     launches_before = lib.qw_gpu_kernel_launches(gpu.handle)
+    wall0 = time.time()
     seconds = timed(step, args.steps)
+    sampler.window(wall0, time.time())
     launches = lib.qw_gpu_kernel_launches(gpu.handle) - launches_before
-    clocks = sampler.stop() if rank == 0 else None
 
     flops_step = w.flops_per_layer() * w.layers          # all heads, whole job
     value = flops_step * args.steps / seconds / 1e12
@@ -316,8 +335,11 @@ def run_product(args):
                 gpu.handle, q_work, k_work, qt, kt, wqt, wkt, runner.cos, runner.sin, w.batch,
                 w.rows, heads_local, 128, workloads.EPS), "prologue")
 
+    wall0 = time.time()
     attn_s = timed(attention_only, args.steps) / (args.steps * w.layers)
     prol_s = timed(prologue_only, args.steps) / (args.steps * w.layers)
+    sampler.window(wall0, time.time())
+    clocks = sampler.stop() if rank == 0 else None
     flops_launch = w.flops_per_layer() / world
     attn_tflops = flops_launch / attn_s / 1e12
     prol_bytes = (2 * n_local * 2 * 2) + 2 * w.rows * 64 * 4

@@ -22,8 +22,8 @@
 
 namespace {
 
-// (128-thread CTAs: the row copy plus the prefetched modulation vectors take about
-// 160 registers per thread, and three such CTAs still fit on an SM)
+// (128-thread CTAs: the row copy plus the prefetched modulation vectors take up to
+// about 150 registers per thread, and three to four such CTAs fit on an SM)
 constexpr int kWarpsPerBlock = 4;
 constexpr int kMaxVecs = 16;  // 16-byte vectors per lane: rows up to 32 * 16 * 8 = 4096 columns
 
@@ -55,64 +55,69 @@ struct NormArgs {
     float epsilon;
 };
 
-// width % 8 == 0 and width <= 32 * kMaxVecs * 8.
+// width % 8 == 0 and width <= 32 * kVecs * 8.  A warp walks rows (stride = warps
+// in the grid); the grid holds a few resident CTAs per SM, so no time goes into
+// launching a CTA per handful of rows.
+template <int kVecs>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 qw_layer_norm_mod_kernel(const NormArgs a) {
-    const uint32_t row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (row >= a.rows) return;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t vecs = a.width >> 3;  // 16-byte vectors per row
-    const uint4 *src = reinterpret_cast<const uint4 *>(a.in + (size_t)row * a.width);
-    uint4 x[kMaxVecs];
+    const uint32_t warps = gridDim.x * kWarpsPerBlock;
+    for (uint32_t row = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); row < a.rows;
+         row += warps) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.in + (size_t)row * a.width);
+        uint4 x[kVecs];
 #pragma unroll
-    for (int i = 0; i < kMaxVecs; ++i) {
-        const uint32_t v = lane + 32u * i;
-        x[i] = v < vecs ? __ldcs(src + v) : make_uint4(0, 0, 0, 0);
-    }
-    const uint32_t map = a.row_map[row];
-    const uint4 *scale = reinterpret_cast<const uint4 *>(
-        a.modulation + ((size_t)map * a.slots + a.scale_slot) * a.width);
+        for (int i = 0; i < kVecs; ++i) {
+            const uint32_t v = lane + 32u * i;
+            x[i] = v < vecs ? __ldcs(src + v) : make_uint4(0, 0, 0, 0);
+        }
+        const uint32_t map = a.row_map[row];
+        const uint4 *scale = reinterpret_cast<const uint4 *>(
+            a.modulation + ((size_t)map * a.slots + a.scale_slot) * a.width);
 
-    float sum = 0.0f;
+        float sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kMaxVecs; ++i) {
-        const uint32_t w[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) sum += bf16_lo(w[k]) + bf16_hi(w[k]);
-    }
-    const float mean = warp_sum(sum) / (float)a.width;
-    float square = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kMaxVecs; ++i) {
-        if (lane + 32u * i < vecs) {  // padding vectors hold zeros, not (0 - mean)
+        for (int i = 0; i < kVecs; ++i) {
             const uint32_t w[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float c0 = bf16_lo(w[k]) - mean, c1 = bf16_hi(w[k]) - mean;
-                square = fmaf(c0, c0, square);
-                square = fmaf(c1, c1, square);
+            for (int k = 0; k < 4; ++k) sum += bf16_lo(w[k]) + bf16_hi(w[k]);
+        }
+        const float mean = warp_sum(sum) / (float)a.width;
+        float square = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kVecs; ++i) {
+            if (lane + 32u * i < vecs) {  // padding vectors hold zeros, not (0 - mean)
+                const uint32_t w[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float c0 = bf16_lo(w[k]) - mean, c1 = bf16_hi(w[k]) - mean;
+                    square = fmaf(c0, c0, square);
+                    square = fmaf(c1, c1, square);
+                }
             }
         }
-    }
-    const float inverse = rsqrtf(warp_sum(square) / (float)a.width + a.epsilon);
+        const float inverse = rsqrtf(warp_sum(square) / (float)a.width + a.epsilon);
 
-    uint4 *dst = reinterpret_cast<uint4 *>(a.out + (size_t)row * a.width);
+        uint4 *dst = reinterpret_cast<uint4 *>(a.out + (size_t)row * a.width);
 #pragma unroll
-    for (int i = 0; i < kMaxVecs; ++i) {
-        const uint32_t v = lane + 32u * i;
-        if (v < vecs) {
-            const uint4 s = __ldg(scale + v);
-            const uint32_t w[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
-            const uint32_t g[4] = {s.x, s.y, s.z, s.w};
-            uint32_t o[4];
+        for (int i = 0; i < kVecs; ++i) {
+            const uint32_t v = lane + 32u * i;
+            if (v < vecs) {
+                const uint4 s = __ldg(scale + v);
+                const uint32_t w[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+                const uint32_t g[4] = {s.x, s.y, s.z, s.w};
+                uint32_t o[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float n0 = __fmul_rn(__fsub_rn(bf16_lo(w[k]), mean), inverse);
-                const float n1 = __fmul_rn(__fsub_rn(bf16_hi(w[k]), mean), inverse);
-                o[k] = pack_bf16(__fmul_rn(n0, __fadd_rn(1.0f, bf16_lo(g[k]))),
-                                 __fmul_rn(n1, __fadd_rn(1.0f, bf16_hi(g[k]))));
+                for (int k = 0; k < 4; ++k) {
+                    const float n0 = __fmul_rn(__fsub_rn(bf16_lo(w[k]), mean), inverse);
+                    const float n1 = __fmul_rn(__fsub_rn(bf16_hi(w[k]), mean), inverse);
+                    o[k] = pack_bf16(__fmul_rn(n0, __fadd_rn(1.0f, bf16_lo(g[k]))),
+                                     __fmul_rn(n1, __fadd_rn(1.0f, bf16_hi(g[k]))));
+                }
+                __stcs(dst + v, make_uint4(o[0], o[1], o[2], o[3]));
             }
-            __stcs(dst + v, make_uint4(o[0], o[1], o[2], o[3]));
         }
     }
 }
@@ -198,7 +203,8 @@ bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
 }  // namespace
 
-extern "C" int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *a, qwcu_stream stream_) {
+extern "C" int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *a, int sm_count,
+                                          qwcu_stream stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (!a->rows || !a->width) return (int)cudaErrorInvalidValue;
     NormArgs k;
@@ -214,10 +220,22 @@ extern "C" int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *a, qwcu_strea
     const unsigned blocks = (a->rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
     const bool vector = a->width % 8 == 0 && a->width <= 32u * kMaxVecs * 8u &&
                         aligned16(k.in) && aligned16(k.out) && aligned16(k.modulation);
-    if (vector)
-        qw_layer_norm_mod_kernel<<<blocks, kWarpsPerBlock * 32, 0, stream>>>(k);
-    else
+    if (!vector) {
         qw_layer_norm_mod_generic_kernel<<<blocks, kWarpsPerBlock * 32, 0, stream>>>(k);
+        return (int)cudaGetLastError();
+    }
+    // A few resident CTAs per SM, each warp walking rows.
+    const unsigned cap = (unsigned)(sm_count > 0 ? sm_count : 148) * 4u;
+    const unsigned grid = blocks < cap ? blocks : cap;
+    const uint32_t vecs_per_lane = (a->width / 8 + 31) / 32;
+    if (vecs_per_lane <= 4)
+        qw_layer_norm_mod_kernel<4><<<grid, kWarpsPerBlock * 32, 0, stream>>>(k);
+    else if (vecs_per_lane <= 8)
+        qw_layer_norm_mod_kernel<8><<<grid, kWarpsPerBlock * 32, 0, stream>>>(k);
+    else if (vecs_per_lane <= 12)
+        qw_layer_norm_mod_kernel<12><<<grid, kWarpsPerBlock * 32, 0, stream>>>(k);
+    else
+        qw_layer_norm_mod_kernel<kMaxVecs><<<grid, kWarpsPerBlock * 32, 0, stream>>>(k);
     return (int)cudaGetLastError();
 }
 

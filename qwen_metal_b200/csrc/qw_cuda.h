@@ -120,7 +120,7 @@ typedef struct {
     float epsilon; /* norm only */
 } qwcu_rowwise_args;
 
-int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *args, qwcu_stream stream);
+int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *args, int sm_count, qwcu_stream stream);
 int qwcu_gate_launch(const qwcu_rowwise_args *args, int sm_count, qwcu_stream stream);
 
 /* h3 causal variant helper: out = bf16(in * scale), elementwise. */

@@ -80,7 +80,7 @@ int qw_gpu_layer_norm_mod_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
     if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
     qwcu_rowwise_args args = {input->dev, NULL, modulation->dev, row_map->dev, output->dev,
                               rows, width, slots, scale_slot, epsilon};
-    int rc = qwcu_layer_norm_mod_launch(&args, gpu->stream);
+    int rc = qwcu_layer_norm_mod_launch(&args, qwcu_device_sm_count(gpu->device), gpu->stream);
     qw_count_launch(gpu, rc, "Qwen AdaLN");
     return rc == 0;
 }

@@ -1,9 +1,10 @@
 #!/usr/bin/env python3
 """Regenerate the golden fixtures under tests/golden/ from a reference checkout.
 
-Run in a container that has the reference project (default /root/reference):
+Run where a checkout of the reference project is present (--ref names it; see the
+default below):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <checkout>]
 
 It writes only small data files next to this script:
 

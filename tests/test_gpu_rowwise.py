@@ -48,9 +48,14 @@ def run_gate(gpu, res, br, mod, row_map, rows, width, slots, slot, in_place=Fals
 
 def check_norm(got, ref):
     # The warp-tree sums differ from the oracle's serial sums in the last fp32 bits and
-    # rsqrt is 1 ulp off 1/sqrt: a bf16 rounding flips by one step now and then.
+    # rsqrt is 1 ulp off 1/sqrt: a bf16 rounding flips by one step now and then.  Where
+    # x - mean cancels to almost nothing, the few-ulp difference of the two means is a
+    # large RELATIVE change of a tiny output: those are held to an absolute bound of
+    # 1e-6 of the row's largest output instead (fp32 has 6e-8 per operation).
     d = bf16_steps(got, ref)
-    assert d.max() <= 1, int(d.max())
+    a, b = O.bf16_to_f32(got), O.bf16_to_f32(ref)
+    tiny = np.abs(a - b) <= 1e-6 * np.abs(b).max(axis=1, keepdims=True)
+    assert ((d <= 1) | tiny).all(), int(d[~tiny].max())
     assert (d > 0).mean() < 5e-3, float((d > 0).mean())
 
 
