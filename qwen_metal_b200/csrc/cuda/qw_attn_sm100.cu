@@ -804,7 +804,12 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
     const uint32_t where = 3u << 16;
     uint32_t t = 0;
     bool ok = true;
-    for (int j = next_tile(ctl, -1, n_max); j < n_max && ok; j = next_tile(ctl, j, n_max)) {
+    int j = next_tile(ctl, -1, n_max);
+    // K and V of the first visited tile are already on their way (ring slots 0, 1):
+    // the kernel body issued them before the row limits were known.
+    t = 2;
+    if (j < n_max) j = next_tile(ctl, j, n_max);
+    for (; j < n_max && ok; j = next_tile(ctl, j, n_max)) {
         for (int which = 0; which < 2 && ok; ++which) {
             uint32_t slot = t % kStages, par = ((t / kStages) & 1u) ^ 1u;
             ok = mbar_wait(ctl, &ctl->bars[kBarKvEmpty + slot], par, p.status,
@@ -831,6 +836,20 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
     }
 }
 
+__device__ __forceinline__ void issue_q_loads(const KernelParams &p, SharedControl *ctl,
+                                              uint8_t *smem_q, const CUtensorMap *map_q, uint32_t b,
+                                              uint32_t h, uint32_t row0) {
+    for (int i = 0; i < 2; ++i) {
+        uint32_t r = row0 + (uint32_t)i * kTileM;
+        if (r >= p.q_rows) continue;  // inactive sub-tile: n_tiles is 0, nobody waits
+        unsigned long long *bar = &ctl->bars[kBarQFull + i];
+        mbar_expect_tx(bar, kTileBytes);
+        uint8_t *dst = smem_q + (size_t)i * kTileBytes;
+        tma_load_3d(dst, map_q, bar, (int)(h * kHeadDim), (int)r, (int)b);
+        tma_load_3d(dst + kHalfTileBytes, map_q, bar, (int)(h * kHeadDim) + 64, (int)r, (int)b);
+    }
+}
+
 template <int kPoly>
 __global__ void __launch_bounds__(kThreads, 1)
 qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -853,7 +872,9 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t qblock = gridDim.x - 1 - blockIdx.x;
     const uint32_t row0 = qblock * (2 * kTileM);
 
-    if (tid == 0) {
+    // The producer thread sets the barriers up itself and starts Q and the first
+    // K/V tile at once, under the row-limit loads of the softmax threads.
+    if (warp == kTmaWarp && lane == 0) {
         for (int i = 0; i < 2; ++i) mbar_init(&ctl->bars[kBarQFull + i], 1);
         for (int i = 0; i < kStages; ++i) {
             mbar_init(&ctl->bars[kBarKvFull + i], 1);
@@ -876,6 +897,19 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         ctl->skip_lo = lo;
         ctl->skip_hi = hi;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        issue_q_loads(p, ctl, smem_q, &map_q, b, h, row0);
+        // First visited key tile, assuming the unit has one (if it has none the
+        // tile is simply never consumed; the producer drains it before exit).
+        const int j0 = lo == 0 ? hi : 0;
+        for (int which = 0; which < 2; ++which) {
+            uint8_t *dst = smem_kv + (size_t)which * kTileBytes;
+            unsigned long long *bar = &ctl->bars[kBarKvFull + which];
+            mbar_expect_tx(bar, kTileBytes);
+            const CUtensorMap *map = which ? &map_v : &map_k;
+            const int col = (int)(kvh * kHeadDim);
+            tma_load_3d(dst, map, bar, col, j0 * kTileN, (int)b);
+            tma_load_3d(dst + kHalfTileBytes, map, bar, col + 64, j0 * kTileN, (int)b);
+        }
     }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -908,18 +942,6 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         int m = 0;
         for (int w = 0; w < 4; ++w) m = max(m, ctl->warp_max[tid * 4 + w]);
         ctl->n_tiles[tid] = (m + kTileN - 1) / kTileN;
-    }
-    // Q does not depend on the limits: start it before the second barrier.
-    if (warp == kTmaWarp && lane == 0) {
-        for (int i = 0; i < 2; ++i) {
-            uint32_t r = row0 + (uint32_t)i * kTileM;
-            if (r >= p.q_rows) continue;  // inactive sub-tile: n_tiles is 0, nobody waits
-            unsigned long long *bar = &ctl->bars[kBarQFull + i];
-            mbar_expect_tx(bar, kTileBytes);
-            uint8_t *dst = smem_q + (size_t)i * kTileBytes;
-            tma_load_3d(dst, &map_q, bar, (int)(h * kHeadDim), (int)r, (int)b);
-            tma_load_3d(dst + kHalfTileBytes, &map_q, bar, (int)(h * kHeadDim) + 64, (int)r, (int)b);
-        }
     }
     __syncthreads();
 
