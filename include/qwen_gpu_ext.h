@@ -144,8 +144,10 @@ void qw_gpu_host_free(void *pointer);
  * context's stream; complete after the next h3_gpu_submit(). */
 int qw_gpu_tensor_read_async(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host,
                              size_t elements);
-/* Select the attention kernel: "sm100" (default) or "scalar" (diagnostic
- * fp32 kernel).  Returns 0 on an unknown name. */
+/* Select the attention kernel: "sm100" (default; the 256-row blocks of the last,
+ * partly filled wave of CTAs run split in two), "sm100-whole" (same kernel, no
+ * block is ever split) or "scalar" (diagnostic fp32 kernel).  Returns 0 on an
+ * unknown name. */
 int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name);
 /* Launches enqueued by this context's ops since creation (own kernels only). */
 uint64_t qw_gpu_kernel_launches(const h3_gpu *gpu);

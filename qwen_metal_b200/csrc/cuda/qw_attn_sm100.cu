@@ -27,6 +27,14 @@
 // output through peer-mapped pointers, so the per-layer gather costs no extra
 // pass: the transfer is issued tile by tile while other tiles still compute.
 //
+// Wave tail.  The grid is one CTA per (batch, head, 256-row block), heaviest
+// blocks first, and rarely a multiple of the SM count.  The units that would
+// form the last, partly filled wave are therefore run in split form, two CTAs per
+// unit: a CTA takes 128 of the rows and gives each of its two sub-tiles half of
+// the key tiles; at the end warpgroup 0 merges the two accumulators (both sit in
+// the same TMEM lanes) with the usual exp2 reweighting.  Twice the CTAs of half
+// the length fill the idle SMs, and nothing leaves the CTA unmerged.
+//
 // Every wait is bounded: when one runs out the CTA records where in the status
 // words, raises a shared abort flag that all other waits poll, drains its TMA
 // loads, frees its TMEM and returns.
@@ -82,7 +90,8 @@ enum Barrier : int {
     kBarOFinal = kBarPFull + 2,           // 2: last P V of sub-tile i complete
     kBarDebug = kBarOFinal + 2,           // trace builds: group completion probe
     kBarEpi = kBarDebug + 1,              // 2: output tile of sub-tile i staged in shared memory
-    kBarCount = kBarEpi + 2
+    kBarMerge = kBarEpi + 2,              // split form: sub-tile 1 published its exponent and row sum
+    kBarCount = kBarMerge + 1
 };
 
 struct __align__(16) SharedControl {
@@ -92,6 +101,12 @@ struct __align__(16) SharedControl {
     int n_tiles[2];      // key tiles each sub-tile needs (by its largest limit)
     int warp_max[8];     // per softmax warp: largest limit
     int skip_lo, skip_hi;  // key tiles [skip_lo, skip_hi) lie inside the padding window
+    // Visited key tiles (the padding window taken out) are numbered 0, 1, ...;
+    // sub-tile i walks tile_count[i] of them from tile_first[i].  Whole form: both
+    // from 0.  Split form: the two halves of one list.
+    int tile_first[2], tile_count[2];
+    float merge_m[kTileM];  // split form: sub-tile 1's reference exponent and row sum
+    float merge_l[kTileM];
 };
 
 constexpr size_t kSmemData = (size_t)(2 + kStages) * kTileBytes;
@@ -117,6 +132,9 @@ struct KernelParams {
     // head count of the destination rows and out_head_offset this rank's first head.
     __nv_bfloat16 *out_peers[8];
     uint32_t n_out, out_heads_total, out_head_offset;
+    // Launch geometry: CTA c < total_units - tail_units runs unit c whole; the
+    // last tail_units units run in split form, two CTAs each.
+    uint32_t n_qblocks, total_units, tail_units;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -164,7 +182,7 @@ __device__ __forceinline__ bool mbar_wait_slow(SharedControl *ctl, unsigned long
             if (atomicCAS(status, 0u, (uint32_t)QWCU_STATUS_WAIT_TIMEOUT) == 0u) {
                 status[1] = where;
                 status[2] = tile;
-                status[3] = blockIdx.x | (blockIdx.y << 12) | (blockIdx.z << 24);
+                status[3] = blockIdx.x;
             }
             __threadfence();
             return false;
@@ -402,8 +420,14 @@ __device__ __forceinline__ int row_limit(const KernelParams &p, uint32_t b, uint
     return min(limit, (int)p.kv_rows);
 }
 
-__device__ __forceinline__ bool tile_skipped(const SharedControl *ctl, int j) {
-    return j >= ctl->skip_lo && j < ctl->skip_hi;
+// Visited tile u -> key tile index, and how many of `tiles` key tiles are visited.
+__device__ __forceinline__ int phys_tile(const SharedControl *ctl, int u) {
+    return u < ctl->skip_lo ? u : u + (ctl->skip_hi - ctl->skip_lo);
+}
+__device__ __forceinline__ int visited_tiles(int tiles, int lo, int hi) {
+    if (tiles <= lo) return tiles;
+    if (tiles >= hi) return tiles - (hi - lo);
+    return lo;
 }
 
 // ---------------------------------------------------------------------------
@@ -413,7 +437,7 @@ template <int kPoly>
 __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedControl *ctl,
                                              const OutMaps &maps_out, uint8_t *stage, int sub,
                                              int tid_in_group, int my_limit, uint32_t b, uint32_t h,
-                                             uint32_t row, uint32_t tile_row0) {
+                                             uint32_t row, uint32_t tile_row0, bool split) {
     const int warp_in_group = tid_in_group >> 5;
     const uint32_t lane_base = (uint32_t)(warp_in_group * 32) << 16;
     const uint32_t tmem = ctl->tmem_base;
@@ -421,7 +445,6 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     const uint32_t tmem_o = tmem + lane_base + (sub ? kTmemO1 : kTmemO0);
     unsigned long long *bar_s = &ctl->bars[kBarSFull + sub];
     unsigned long long *bar_p = &ctl->bars[kBarPFull + sub];
-    const int n_tiles = ctl->n_tiles[sub];
     const int pad_lo = p.text_pad ? (int)p.text_len[b] : 0;
     const int pad_hi = (int)p.text_pad;
     const float c = p.scale_log2;
@@ -435,8 +458,9 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     bool ok = true;
     int processed = 0;
 
-    for (int j = 0; j < n_tiles && ok; ++j) {
-        if (tile_skipped(ctl, j)) continue;
+    const int u_first = ctl->tile_first[sub], u_end = u_first + ctl->tile_count[sub];
+    for (int u = u_first; u < u_end && ok; ++u) {
+        const int j = phys_tile(ctl, u);
         ok = mbar_wait(ctl, bar_s, phase, p.status, (1u << 16) | (uint32_t)(kBarSFull + sub),
                        (uint32_t)j);
         if (!ok) break;
@@ -558,89 +582,122 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     // goes to every peer's output over NVLink in bulk instead of 64-byte pieces.
     if (!ok || tile_row0 >= p.q_rows) return;  // gave up, or this sub-tile holds no rows
     const bool has_row = row < p.q_rows;
-    const float inv_l = l_run > 0.0f ? 1.0f / l_run : 0.0f;
     if (processed > 0) {
         ok = mbar_wait(ctl, &ctl->bars[kBarOFinal + sub], 0, p.status,
                        (1u << 16) | (uint32_t)(kBarOFinal + sub), 0xffffu);
         if (!ok) return;
         tc_fence_after();
-    } else if (!p.head_major_out) {
+    }
+    // Scale factors of the accumulators that make up the output rows: O_sub alone,
+    // or in split form O_0 and O_1 brought to a common reference exponent.
+    // out = (w_own * O_own + w_other * O_other) * inv: the weights are exactly 1 when
+    // the reference exponents agree, so a split block of equal-score rows merges
+    // exactly like the whole block would have summed.
+    float w_own = 1.0f, w_other = 0.0f, inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    bool use_own = processed > 0, use_other = false;
+    if (split) {
+        const float m_own = (processed > 0 && m_ref != -INFINITY) ? m_ref * fabsf(c) : -INFINITY;
+        if (sub == 1) {
+            // Publish exponent and row sum; warpgroup 0 reads O_1 itself (same lanes).
+            ctl->merge_m[tid_in_group] = m_own;
+            ctl->merge_l[tid_in_group] = l_run;
+            __syncwarp();
+            if ((tid_in_group & 31) == 0) mbar_arrive(&ctl->bars[kBarMerge]);
+            return;
+        }
+        ok = mbar_wait(ctl, &ctl->bars[kBarMerge], 0, p.status, (1u << 16) | (uint32_t)kBarMerge,
+                       0xfffbu);
+        if (!ok) return;
+        use_other = ctl->tile_count[1] > 0;
+        if (use_other) {
+            ok = mbar_wait(ctl, &ctl->bars[kBarOFinal + 1], 0, p.status,
+                           (1u << 16) | (uint32_t)(kBarOFinal + 1), 0xfffeu);
+            if (!ok) return;
+            tc_fence_after();
+        }
+        const float m_other = ctl->merge_m[tid_in_group], l_other = ctl->merge_l[tid_in_group];
+        const float m_all = fmaxf(m_own, m_other);
+        const float a_own = m_own == -INFINITY ? 0.0f : fast_exp2(m_own - m_all);
+        const float a_other = m_other == -INFINITY ? 0.0f : fast_exp2(m_other - m_all);
+        const float l_all = a_own * l_run + a_other * l_other;
+        inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+        w_own = a_own;
+        w_other = a_other;
+    } else if (processed == 0 && !p.head_major_out) {
         // Nothing was computed for this sub-tile (zeros go out), but its Q load may
         // still be in flight into the staging area: let it land first.
         ok = mbar_wait(ctl, &ctl->bars[kBarQFull + sub], 0, p.status,
                        (1u << 16) | (uint32_t)(kBarQFull + sub), 0xfffdu);
         if (!ok) return;
     }
-    if (p.head_major_out) {
-        // (every lane takes part in the warp-collective TMEM loads; only the
-        // stores depend on the row being real)
-        __nv_bfloat16 *dst =
-            p.out + (((size_t)b * p.heads + h) * p.q_rows + (has_row ? row : 0u)) * kHeadDim;
-#pragma unroll 1
-        for (int chunk = 0; chunk < 4; ++chunk) {
-            uint32_t o[32];
-            if (processed > 0) {
-                QW_TMEM_LD32(tmem_o + chunk * 32, o);
-                tmem_wait_ld();
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (processed > 0) {
-                    v.x = pack_bf16(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                    v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                    v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                    v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                }
-                if (has_row) reinterpret_cast<uint4 *>(dst + chunk * 32)[i >> 3] = v;
-            }
-        }
-        return;
+    if (split && !p.head_major_out && !use_own) {
+        // (same reason: the shared Q tile is the staging area)
+        ok = mbar_wait(ctl, &ctl->bars[kBarQFull + 0], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarQFull + 0), 0xfffdu);
+        if (!ok) return;
     }
-    {
-        // Row r of the tile: two 128-byte lines (columns 0..63 and 64..127, one
-        // half tile apart), 16-byte chunks XOR-swizzled by the row like TMA does.
-        const int r = tid_in_group;
-        uint8_t *line = stage + r * 128;
-        const int sw = r & 7;
+    const uint32_t tmem_other = tmem + lane_base + kTmemO1;
+    // Row r of the tile in the staging area: two 128-byte lines (columns 0..63 and
+    // 64..127, one half tile apart), 16-byte chunks XOR-swizzled by the row like TMA
+    // does.  Head-major output is written directly.  (Every lane takes part in the
+    // warp-collective TMEM loads; only the stores depend on the row being real.)
+    uint8_t *line = stage + tid_in_group * 128;
+    const int sw = tid_in_group & 7;
+    __nv_bfloat16 *direct =
+        p.out + (((size_t)b * p.heads + h) * p.q_rows + (has_row ? row : 0u)) * kHeadDim;
 #pragma unroll 1
-        for (int chunk = 0; chunk < 4; ++chunk) {
-            uint32_t o[32];
-            if (processed > 0) {
-                QW_TMEM_LD32(tmem_o + chunk * 32, o);
-                tmem_wait_ld();
-            }
+    for (int chunk = 0; chunk < 4; ++chunk) {
+        float v[32];
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (processed > 0) {
-                    v.x = pack_bf16(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                    v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                    v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                    v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                }
-                const int c = chunk * 4 + (i >> 3);  // 16-byte chunk of the 256-byte row
-                *reinterpret_cast<uint4 *>(line + (c >> 3) * kHalfTileBytes + (((c & 7) ^ sw) << 4)) = v;
+        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+        if (use_own) {
+            uint32_t o[32];
+            QW_TMEM_LD32(tmem_o + chunk * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]) * w_own;
+        }
+        if (use_other) {
+            uint32_t o[32];
+            QW_TMEM_LD32(tmem_other + chunk * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = fmaf(__uint_as_float(o[i]), w_other, v[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+            uint4 packed;
+            packed.x = pack_bf16(v[i] * inv, v[i + 1] * inv);
+            packed.y = pack_bf16(v[i + 2] * inv, v[i + 3] * inv);
+            packed.z = pack_bf16(v[i + 4] * inv, v[i + 5] * inv);
+            packed.w = pack_bf16(v[i + 6] * inv, v[i + 7] * inv);
+            if (p.head_major_out) {
+                if (has_row) reinterpret_cast<uint4 *>(direct + chunk * 32)[i >> 3] = packed;
+            } else {
+                const int c16 = chunk * 4 + (i >> 3);  // 16-byte chunk of the 256-byte row
+                *reinterpret_cast<uint4 *>(line + (c16 >> 3) * kHalfTileBytes +
+                                           (((c16 & 7) ^ sw) << 4)) = packed;
             }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> TMA reads
-        __syncwarp();
-        if ((tid_in_group & 31) == 0) mbar_arrive(&ctl->bars[kBarEpi + sub]);
-        if (tid_in_group == 0) {
-            if (!mbar_wait(ctl, &ctl->bars[kBarEpi + sub], 0, p.status,
-                           (1u << 16) | (uint32_t)(kBarEpi + sub), 0xfffcu))
-                return;
-            const int col = (int)((p.out_head_offset + h) * kHeadDim);
-            for (uint32_t d = 0; d < p.n_out; ++d) {
-                tma_store_3d(&maps_out.m[d], stage, col, (int)tile_row0, (int)b);
-                tma_store_3d(&maps_out.m[d], stage + kHalfTileBytes, col + 64, (int)tile_row0, (int)b);
-            }
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            // Shared memory may be released once the stores have read it; the
-            // writes themselves are complete when the grid completes, which is
-            // what the barrier behind a sharded launch waits for.
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+    if (p.head_major_out) return;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> TMA reads
+    __syncwarp();
+    if ((tid_in_group & 31) == 0) mbar_arrive(&ctl->bars[kBarEpi + sub]);
+    if (tid_in_group == 0) {
+        if (!mbar_wait(ctl, &ctl->bars[kBarEpi + sub], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarEpi + sub), 0xfffcu))
+            return;
+        const int col = (int)((p.out_head_offset + h) * kHeadDim);
+        for (uint32_t d = 0; d < p.n_out; ++d) {
+            tma_store_3d(&maps_out.m[d], stage, col, (int)tile_row0, (int)b);
+            tma_store_3d(&maps_out.m[d], stage + kHalfTileBytes, col + 64, (int)tile_row0, (int)b);
         }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        // Shared memory may be released once the stores have read it; the
+        // writes themselves are complete when the grid completes, which is
+        // what the barrier behind a sharded launch waits for.
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 }
 
@@ -678,17 +735,12 @@ __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint3
     }
 }
 
-__device__ __forceinline__ int next_tile(const SharedControl *ctl, int j, int n_max) {
-    ++j;
-    if (j >= ctl->skip_lo && j < ctl->skip_hi) j = ctl->skip_hi;
-    return j < n_max ? j : n_max;
-}
-
 __device__ __forceinline__ void mma_role(const KernelParams &p, SharedControl *ctl,
                                          uint8_t *smem_q, uint8_t *smem_kv) {
-    const int n0 = ctl->n_tiles[0], n1 = ctl->n_tiles[1];
+    // Whole form: both sub-tiles walk the visited tiles from 0; u counts them.
+    const int n0 = ctl->tile_count[0], n1 = ctl->tile_count[1];
     const int n_max = max(n0, n1);
-    int j = next_tile(ctl, -1, n_max);
+    int j = 0;
     if (j >= n_max) return;
     const uint32_t tmem = ctl->tmem_base;
     // Low descriptor words: start address in 16-byte units plus the fixed LBO field.
@@ -727,7 +779,7 @@ __device__ __forceinline__ void mma_role(const KernelParams &p, SharedControl *c
         tc_commit(&ctl->bars[kBarKvEmpty + slot]);
     }
     while (j < n_max) {
-        const int jn = next_tile(ctl, j, n_max);
+        const int jn = j + 1;
         uint32_t v_slot = t % kStages, v_par = (t / kStages) & 1u;
         ++t;
         uint32_t k_slot = 0, k_par = 0;
@@ -794,22 +846,93 @@ __device__ __forceinline__ void mma_role(const KernelParams &p, SharedControl *c
     tc_commit(&ctl->bars[kBarOFinal + 1]);
 }
 
+// Split form: sub-tile 0 walks visited tiles [0, la), sub-tile 1 [la, la + lb),
+// both against the one Q tile.  K/V pairs are loaded in the order a0 b0 a1 b1 ...
+// (pair = K then V, one ring slot each); slot_of() gives the ring position of a
+// pair's K, its V follows.
+__device__ __forceinline__ uint32_t pair_a(int s, int lb) { return 2u * (uint32_t)(s + min(s, lb)); }
+__device__ __forceinline__ uint32_t pair_b(int s) { return 2u * (uint32_t)(2 * s + 1); }
+
+__device__ __forceinline__ void mma_role_split(const KernelParams &p, SharedControl *ctl,
+                                               uint8_t *smem_q, uint8_t *smem_kv) {
+    const int la = ctl->tile_count[0], lb = ctl->tile_count[1];
+    if (la <= 0) return;
+    const uint32_t tmem = ctl->tmem_base;
+    const uint32_t q_lo = (smem_u32(smem_q) >> 4) | kDescLoKMajor;
+    const uint32_t kv_lo = smem_u32(smem_kv) >> 4;
+    const uint32_t s_tmem[2] = {tmem + kTmemS0, tmem + kTmemS1};
+    const uint32_t o_tmem[2] = {tmem + kTmemO0, tmem + kTmemO1};
+    const uint32_t where = 2u << 16;
+    uint32_t p_phase[2] = {0, 0};
+
+    // Waits for ring position t, returns the low descriptor word of its slot.
+#define QW_RING_WAIT(t_, lo_fixed_, out_)                                                       \
+    {                                                                                           \
+        const uint32_t slot_ = (t_) % kStages, par_ = ((t_) / kStages) & 1u;                    \
+        if (!mbar_wait(ctl, &ctl->bars[kBarKvFull + slot_], par_, p.status,                     \
+                       where | (kBarKvFull + slot_), (uint32_t)(t_)))                           \
+            return;                                                                             \
+        tc_fence_after();                                                                       \
+        out_ = (kv_lo + slot_ * (kTileBytes >> 4)) | (lo_fixed_);                               \
+    }
+#define QW_RING_FREE(t_) tc_commit(&ctl->bars[kBarKvEmpty + ((t_) % kStages)])
+
+    if (!mbar_wait(ctl, &ctl->bars[kBarQFull + 0], 0, p.status, where | kBarQFull, 0)) return;
+    uint32_t desc;
+    QW_RING_WAIT(pair_a(0, lb), kDescLoKMajor, desc);
+    issue_qk(s_tmem[0], q_lo, desc);
+    tc_commit(&ctl->bars[kBarSFull + 0]);
+    QW_RING_FREE(pair_a(0, lb));
+    if (lb > 0) {
+        QW_RING_WAIT(pair_b(0), kDescLoKMajor, desc);
+        issue_qk(s_tmem[1], q_lo, desc);
+        tc_commit(&ctl->bars[kBarSFull + 1]);
+        QW_RING_FREE(pair_b(0));
+    }
+    for (int s = 0; s < la; ++s) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int count = i ? lb : la;
+            if (s >= count) continue;
+            const uint32_t t_now = i ? pair_b(s) : pair_a(s, lb);
+            QW_RING_WAIT(t_now + 1, kDescLoVMajor, desc);
+            if (!mbar_wait(ctl, &ctl->bars[kBarPFull + i], p_phase[i], p.status,
+                           where | (kBarPFull + i), (uint32_t)s))
+                return;
+            p_phase[i] ^= 1u;
+            tc_fence_after();
+            issue_pv(o_tmem[i], s_tmem[i], desc, s > 0);
+            QW_RING_FREE(t_now + 1);
+            if (s + 1 < count) {
+                const uint32_t t_next = i ? pair_b(s + 1) : pair_a(s + 1, lb);
+                QW_RING_WAIT(t_next, kDescLoKMajor, desc);
+                issue_qk(s_tmem[i], q_lo, desc);
+                tc_commit(&ctl->bars[kBarSFull + i]);
+                QW_RING_FREE(t_next);
+            }
+        }
+    }
+#undef QW_RING_WAIT
+#undef QW_RING_FREE
+    tc_commit(&ctl->bars[kBarOFinal + 0]);
+    tc_commit(&ctl->bars[kBarOFinal + 1]);
+}
+
 // ---------------------------------------------------------------------------
 // TMA producer role (one thread).
 // ---------------------------------------------------------------------------
 __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *smem_kv,
                          const CUtensorMap *map_k, const CUtensorMap *map_v, uint32_t b,
-                         uint32_t kvh) {
-    const int n_max = max(ctl->n_tiles[0], ctl->n_tiles[1]);
+                         uint32_t kvh, bool split) {
     const uint32_t where = 3u << 16;
-    uint32_t t = 0;
-    bool ok = true;
-    int j = next_tile(ctl, -1, n_max);
     // K and V of the first visited tile are already on their way (ring slots 0, 1):
     // the kernel body issued them before the row limits were known.
-    t = 2;
-    if (j < n_max) j = next_tile(ctl, j, n_max);
-    for (; j < n_max && ok; j = next_tile(ctl, j, n_max)) {
+    uint32_t t = 2;
+    bool ok = true;
+    const int col = (int)(kvh * kHeadDim);
+    // One (K, V) pair of visited tile u into the next two ring slots.
+    auto load_pair = [&](int u) {
+        const int j = phys_tile(ctl, u);
         for (int which = 0; which < 2 && ok; ++which) {
             uint32_t slot = t % kStages, par = ((t / kStages) & 1u) ^ 1u;
             ok = mbar_wait(ctl, &ctl->bars[kBarKvEmpty + slot], par, p.status,
@@ -820,9 +943,19 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
             unsigned long long *bar = &ctl->bars[kBarKvFull + slot];
             mbar_expect_tx(bar, kTileBytes);
             const CUtensorMap *map = which ? map_v : map_k;
-            int col = (int)(kvh * kHeadDim);
             tma_load_3d(dst, map, bar, col, j * kTileN, (int)b);
             tma_load_3d(dst + kHalfTileBytes, map, bar, col + 64, j * kTileN, (int)b);
+        }
+    };
+    if (!split) {
+        const int n_max = max(ctl->tile_count[0], ctl->tile_count[1]);
+        for (int u = 1; u < n_max && ok; ++u) load_pair(u);
+    } else {
+        // pairs in the order a0 (under way), b0, a1, b1, ...
+        const int la = ctl->tile_count[0], lb = ctl->tile_count[1];
+        for (int s = 0; s < la && ok; ++s) {
+            if (s > 0) load_pair(s);
+            if (s < lb && ok) load_pair(la + s);
         }
     }
     // Leave no copy in flight: every issued load must have landed before the
@@ -838,8 +971,8 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
 
 __device__ __forceinline__ void issue_q_loads(const KernelParams &p, SharedControl *ctl,
                                               uint8_t *smem_q, const CUtensorMap *map_q, uint32_t b,
-                                              uint32_t h, uint32_t row0) {
-    for (int i = 0; i < 2; ++i) {
+                                              uint32_t h, uint32_t row0, int tiles) {
+    for (int i = 0; i < tiles; ++i) {
         uint32_t r = row0 + (uint32_t)i * kTileM;
         if (r >= p.q_rows) continue;  // inactive sub-tile: n_tiles is 0, nobody waits
         unsigned long long *bar = &ctl->bars[kBarQFull + i];
@@ -865,12 +998,19 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const uint32_t b = blockIdx.z;
-    const uint32_t h = blockIdx.y;
+    // CTA -> unit.  Units are numbered batch-major, then head, then query block
+    // with the heaviest blocks first (rows late in the joint sequence see the most
+    // keys).  The last tail_units units run in split form, two CTAs each.
+    const uint32_t whole_units = p.total_units - p.tail_units;
+    const bool split = blockIdx.x >= whole_units;
+    const uint32_t unit = split ? whole_units + ((blockIdx.x - whole_units) >> 1) : blockIdx.x;
+    const uint32_t half = split ? (blockIdx.x - whole_units) & 1u : 0u;
+    const uint32_t bh = unit / p.n_qblocks;
+    const uint32_t b = bh / p.heads;
+    const uint32_t h = bh - b * p.heads;
     const uint32_t kvh = (uint32_t)((unsigned long long)h * p.kv_heads / p.heads);
-    // Heaviest query blocks first: rows late in the joint sequence see the most keys.
-    const uint32_t qblock = gridDim.x - 1 - blockIdx.x;
-    const uint32_t row0 = qblock * (2 * kTileM);
+    const uint32_t qblock = p.n_qblocks - 1 - (unit - bh * p.n_qblocks);
+    const uint32_t row0 = qblock * (2 * kTileM) + half * kTileM;
 
     // The producer thread sets the barriers up itself and starts Q and the first
     // K/V tile at once, under the row-limit loads of the softmax threads.
@@ -886,6 +1026,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_init(&ctl->bars[kBarOFinal + i], 1);
             mbar_init(&ctl->bars[kBarEpi + i], kTileM / 32);
         }
+        mbar_init(&ctl->bars[kBarMerge], kTileM / 32);
         mbar_init(&ctl->bars[kBarDebug], 1);
         ctl->abort_flag = 0;
         int lo = 0, hi = 0;
@@ -897,7 +1038,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         ctl->skip_lo = lo;
         ctl->skip_hi = hi;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        issue_q_loads(p, ctl, smem_q, &map_q, b, h, row0);
+        issue_q_loads(p, ctl, smem_q, &map_q, b, h, row0, split ? 1 : 2);
         // First visited key tile, assuming the unit has one (if it has none the
         // tile is simply never consumed; the producer drains it before exit).
         const int j0 = lo == 0 ? hi : 0;
@@ -927,7 +1068,8 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     if (tid < kSoftmaxThreads) {
         sub = tid >> 7;
         tid_in_group = tid & 127;
-        my_row = row0 + (uint32_t)sub * kTileM + (uint32_t)tid_in_group;
+        // (split form: both warpgroups work on the same 128 rows)
+        my_row = row0 + (split ? 0u : (uint32_t)sub * kTileM) + (uint32_t)tid_in_group;
         my_limit = row_limit(p, b, my_row);
         int warp_max = my_limit;
 #pragma unroll
@@ -941,24 +1083,39 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     if (tid < 2) {
         int m = 0;
         for (int w = 0; w < 4; ++w) m = max(m, ctl->warp_max[tid * 4 + w]);
-        ctl->n_tiles[tid] = (m + kTileN - 1) / kTileN;
+        const int tiles = (m + kTileN - 1) / kTileN;
+        ctl->n_tiles[tid] = tiles;
+        const int visited = visited_tiles(tiles, ctl->skip_lo, ctl->skip_hi);
+        if (!split) {
+            ctl->tile_first[tid] = 0;
+            ctl->tile_count[tid] = visited;
+        } else {
+            // both warpgroups saw the same rows: the first half (rounded up) and the rest
+            const int first_half = (visited + 1) / 2;
+            ctl->tile_first[tid] = tid ? first_half : 0;
+            ctl->tile_count[tid] = tid ? visited - first_half : first_half;
+        }
     }
     __syncthreads();
 
     if (tid < kSoftmaxThreads) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         softmax_role<kPoly>(p, ctl, maps_out, smem_q + (size_t)sub * kTileBytes, sub, tid_in_group,
-                            my_limit, b, h, my_row, row0 + (uint32_t)sub * kTileM);
+                            my_limit, b, h, my_row, split ? row0 : row0 + (uint32_t)sub * kTileM,
+                            split);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     }
     if (tid < kSoftmaxThreads) {
     } else if (warp == kMmaWarp) {
-        if (lane == 0) mma_role(p, ctl, smem_q, smem_kv);
+        if (lane == 0) {
+            if (split) mma_role_split(p, ctl, smem_q, smem_kv);
+            else mma_role(p, ctl, smem_q, smem_kv);
+        }
     } else if (warp == kTmaWarp && lane == 0) {
-        tma_role(p, ctl, smem_kv, &map_k, &map_v, b, kvh);
+        tma_role(p, ctl, smem_kv, &map_k, &map_v, b, kvh, split);
         // Q loads of active sub-tiles must have landed as well.
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < (split ? 1 : 2); ++i) {
             if (row0 + (uint32_t)i * kTileM >= p.q_rows) continue;
             long long start = clock64();
             while (!mbar_try(&ctl->bars[kBarQFull + i], 0))
@@ -1050,6 +1207,28 @@ void trace_dump(cudaStream_t stream) {
 typedef void (*AttnKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const OutMaps,
                            const KernelParams);
 
+int sm_count_of_current_device() {
+    static int sms[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) {
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (sms[dev] <= 0) sms[dev] = 148;
+    }
+    return sms[dev];
+}
+
+// QW_CUDA_ATTN_TAIL=whole: never split the last wave's units (comparison runs).
+bool whole_units_forced() {
+    static int forced = -1;
+    if (forced < 0) {
+        const char *env = getenv("QW_CUDA_ATTN_TAIL");
+        forced = env && !strcmp(env, "whole") ? 1 : 0;
+    }
+    return forced != 0;
+}
+
 // How many of every 4 score pairs take the polynomial exp2 (QW_CUDA_EXP_POLY=0..4
 // overrides the default for tuning).
 AttnKernel pick_kernel() {
@@ -1129,7 +1308,19 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
         for (uint32_t d = 0; d < p.n_out; ++d)
             if ((rc = make_map(&maps_out.m[d], p.out_peers[d], a->batch, a->q_rows, p.out_heads_total)))
                 return rc;
-    dim3 grid((a->q_rows + 2 * kTileM - 1) / (2 * kTileM), a->heads, a->batch);
+    // One CTA per unit; the units of the last, partly filled wave run split in two
+    // (half the rows each, the key tiles divided between the sub-tiles) when the
+    // doubled CTAs still fit the idle SMs, give or take a few light units.
+    const unsigned long long units =
+        (unsigned long long)((a->q_rows + 2 * kTileM - 1) / (2 * kTileM)) * a->heads * a->batch;
+    if (units > 0x3fffffffull) return (int)cudaErrorInvalidValue;
+    p.n_qblocks = (a->q_rows + 2 * kTileM - 1) / (2 * kTileM);
+    p.total_units = (uint32_t)units;
+    const uint32_t sms = (uint32_t)sm_count_of_current_device();
+    const uint32_t rest = p.total_units % sms;
+    p.tail_units = (!a->whole_units && !whole_units_forced() && rest && 2 * rest <= sms + sms / 16)
+                       ? rest : 0u;
+    const unsigned grid = p.total_units + p.tail_units;
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, maps_out, p);
     rc = (int)cudaGetLastError();
 #ifdef QW_ATTN_TRACE

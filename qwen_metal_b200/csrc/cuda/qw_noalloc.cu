@@ -136,6 +136,7 @@ extern "C" int h3_gpu_gqa_causal_noalloc_bf16(h3_gpu *gpu, h3_gpu_tensor *output
     args.kv_heads = kv_heads;
     args.scale = 1.0f;  // already folded into the query
     args.status = gpu->status_dev;
+    args.whole_units = gpu->attn_kernel == QW_ATTN_SM100_WHOLE;
     rc = gpu->attn_kernel == QW_ATTN_SCALAR ? qwcu_attn_scalar_launch(&args, gpu->stream)
                                             : qwcu_attn_sm100_launch(&args, gpu->stream);
     qw_count_launch(gpu, rc, "GQA (no-alloc)");

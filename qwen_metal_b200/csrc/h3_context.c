@@ -211,6 +211,7 @@ uint64_t qw_gpu_kernel_launches(const h3_gpu *gpu) { return gpu ? gpu->kernel_la
 int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name) {
     if (!gpu || !name) return 0;
     if (!strcmp(name, "sm100")) gpu->attn_kernel = QW_ATTN_SM100;
+    else if (!strcmp(name, "sm100-whole")) gpu->attn_kernel = QW_ATTN_SM100_WHOLE;
     else if (!strcmp(name, "scalar")) gpu->attn_kernel = QW_ATTN_SCALAR;
     else {
         qw_set_error(gpu, "unknown attention kernel '%s'", name);

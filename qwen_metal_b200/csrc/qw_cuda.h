@@ -67,6 +67,9 @@ typedef struct {
     uint32_t out_heads_total;
     uint32_t out_head_offset;
     uint32_t *status; /* QWCU_STATUS_WORDS device words, zero when healthy */
+    /* sm100 kernel: never run the units of the last wave in split form (two CTAs
+     * per 256-row block, key tiles divided between the sub-tiles). */
+    int whole_units;
 } qwcu_attn_args;
 
 /* tcgen05/TMEM/TMA flash-attention forward (sm_100a). */

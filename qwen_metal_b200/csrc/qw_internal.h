@@ -12,7 +12,7 @@
 #include "qwen_attn_host.h"
 #include "qwen_gpu_ext.h"
 
-enum { QW_ATTN_SM100 = 0, QW_ATTN_SCALAR = 1 };
+enum { QW_ATTN_SM100 = 0, QW_ATTN_SCALAR = 1, QW_ATTN_SM100_WHOLE = 2 };
 
 struct h3_gpu {
     int device;

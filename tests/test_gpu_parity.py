@@ -59,7 +59,16 @@ def run_prefix(gpu, q, k, v, limits, q_rows, kv_rows, heads, kv_heads, scale=SCA
     return out.reshape(q_rows, heads, 128)
 
 
-@pytest.fixture(params=["sm100", "scalar"])
+@pytest.fixture(autouse=True)
+def _default_kernel_afterwards(gpu):
+    yield
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+
+
+# "sm100" splits the 256-row blocks of the last wave of CTAs in two (on shapes with
+# fewer blocks than SMs that is every block), "sm100-whole" never does, "scalar" is
+# the fp32 diagnostic kernel.
+@pytest.fixture(params=["sm100", "sm100-whole", "scalar"])
 def kernel(request, gpu):
     assert gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, request.param.encode())
     yield request.param
@@ -232,8 +241,15 @@ def test_cfg1_bidirectional_text_reading(gpu):
     gates(out, oracle_layer(w, inputs), "cfg1 bidirectional text")
 
 
+@pytest.fixture(params=["sm100", "sm100-whole"])
+def tail_form(request, gpu):
+    assert gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, request.param.encode())
+    yield request.param
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+
+
 @pytest.mark.parametrize("index,count", [(3, 192), (4, 160), (5, 96)])
-def test_large_configs_row_sample(gpu, index, count):
+def test_large_configs_row_sample(gpu, tail_form, index, count):
     w = workloads.workload(index)
     inputs, out = run_workload_layer(gpu, w)
     rows = sample_rows(w, count)
@@ -260,8 +276,26 @@ def test_cfg3_sm100_agrees_with_scalar_kernel_everywhere(gpu):
 # --------------------------------------------------------------------------
 # integer mask indexing, bit-exact on the device
 # --------------------------------------------------------------------------
+def test_split_blocks_agree_with_whole_blocks(gpu):
+    """cfg3 with 3 heads (what one of eight GPUs runs): 102 blocks on 148 SMs, so
+    the default splits 46 of them in two.  The merged halves agree with the same
+    blocks run whole within the parity gates (P is rounded to bf16 relative to a
+    reference exponent that depends on where the keys were cut, so not bit for
+    bit), and two runs of the split form are bit-identical."""
+    w = dataclasses.replace(workloads.workload(3), heads=3, prologue=False)
+    _, first = run_workload_layer(gpu, w)
+    _, second = run_workload_layer(gpu, w)
+    assert np.array_equal(first, second)
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100-whole")
+    try:
+        _, whole = run_workload_layer(gpu, w)
+    finally:
+        gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+    gates(first, bf16_to_f32(whole), "split vs whole blocks")
+
+
 @pytest.mark.parametrize("case", ["kat", "cfg3", "ragged"])
-def test_mask_indexing_bit_exact(gpu, case):
+def test_mask_indexing_bit_exact(gpu, tail_form, case):
     """q = 0 makes every visible key weigh exactly 1, V[s, d] = [s % 128 == d]
     makes O[r, d] the count of visible keys in residue class d: the output is
     bf16(count_d * (1 / count)), reproducible exactly from the oracle's dense mask."""
@@ -479,6 +513,7 @@ def test_target_only_layer_matches_full_layer(gpu):
     cache rows) and qw_gpu_sdpa_rect_bf16.  With unchanged inputs the result must
     equal the full layer's target rows bit for bit (same per-row arithmetic), the
     cache must be unchanged outside the target rows, and both must match the oracle."""
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100-whole")  # same form for both runs
     w = workloads.workload(4)
     w = dataclasses.replace(w, heads=4)          # text 256 + condition 4096 + target 4096
     rows, H = w.rows, w.heads
@@ -534,5 +569,13 @@ def test_target_only_layer_matches_full_layer(gpu):
                                                   rows, t_base + 1, t_rows, H, 128, workloads.EPS)
     assert "outside" in gpu.error()
     gpu.submit()
+    # the default form (the few blocks of this shape run split) within the gates
+    gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+    gpu.begin()
+    gpu.check(lib.qw_gpu_sdpa_rect_bf16(gpu.handle, out, tq, kc, vc, t_rows, rows, H, 128, SCALE),
+              "rect attention, default form")
+    gpu.submit()
+    got = gpu.read_bf16(out, t_rows * H * 128).reshape(t_rows, H, 128)
+    gates(got[sample], ref.reshape(t_rows, H, 128)[sample], "target-only layer, default form")
     for t in (qt, kt, vt, wqt, wkt, ct, st, lt, full, kc, vc, tq, tk, tv, tc, ts, out):
         gpu.free(t)
