@@ -233,16 +233,10 @@ __device__ __forceinline__ void tc_commit(unsigned long long *bar) {
                  : "memory");
 }
 
-// Shared-memory matrix descriptor (sm_100 format): 128B swizzle, version 1.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;  // descriptor version
-    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
-    return d;
-}
+// Shared-memory matrix descriptors (sm_100 format) are built as two 32-bit words
+// further down (desc_hi / desc_lo_fixed): start address >> 4 in bits 0-13, leading
+// byte offset >> 4 in bits 16-29, stride byte offset >> 4 in bits 32-45, descriptor
+// version 1 in bit 46, 128B swizzle = 2 in bits 61-63.
 
 // Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, M = 128, N = 128.
 constexpr uint32_t make_idesc(bool b_mn_major) {

@@ -36,9 +36,6 @@ __device__ __forceinline__ uint32_t f32_to_bf16_bits(float v) {
     bits += 0x7fffu + ((bits >> 16) & 1u);
     return bits >> 16;
 }
-__device__ __forceinline__ float round_bf16(float v) {
-    return __uint_as_float(f32_to_bf16_bits(v) << 16);
-}
 
 struct Params {
     const uint4 *q_in;
