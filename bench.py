@@ -130,6 +130,7 @@ def cpu_sample(w, budget_s, chunk_rows=256, seed=17):
     (TFLOP/s over the SDPA sample, description, threads)."""
     import oracle_lib as O
     from qwen_metal_b200 import workloads
+    O.use_all_cores()  # a launcher may have exported OMP_NUM_THREADS=1 to every rank
     q, k, v, wq, wk = workloads.layer_inputs(w, 0)
     cos, sin = w.rope_tables()
     t0 = time.perf_counter()

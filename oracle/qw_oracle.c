@@ -14,6 +14,14 @@
 #include <omp.h>
 #endif
 
+void qwo_set_threads(int threads) {
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}
+
 int qwo_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

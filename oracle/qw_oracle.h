@@ -131,6 +131,9 @@ void qwo_gate_bf16(uint16_t *out, const uint16_t *residual, const uint16_t *bran
                    const uint16_t *modulation, const uint32_t *row_map, uint32_t rows,
                    uint32_t width, uint32_t slots, uint32_t gate_slot);
 
+/* OpenMP threads the loops above use; qwo_set_threads overrides the environment
+ * (a launcher may export OMP_NUM_THREADS=1 to every rank). */
+void qwo_set_threads(int threads);
 int qwo_threads(void);
 
 #ifdef __cplusplus

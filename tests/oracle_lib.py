@@ -76,6 +76,16 @@ def threads():
     return load().qwo_threads()
 
 
+def use_all_cores():
+    """Let the oracle's OpenMP loops use every core this process may run on,
+    whatever OMP_NUM_THREADS says (torchrun exports 1 to each rank)."""
+    lib = load()
+    lib.qwo_set_threads.argtypes = [C.c_int]
+    lib.qwo_set_threads.restype = None
+    lib.qwo_set_threads(len(os.sched_getaffinity(0)))
+    return lib.qwo_threads()
+
+
 def sdpa(q, k, v, limits, batch, q_rows, kv_rows, heads, kv_heads, scale, text_len=None,
          text_pad=0, rows=None, per_batch_limits=False):
     """fp32 oracle output [batch, q_rows, heads, 128]; `rows` = flat b*q_rows+r
