@@ -1248,6 +1248,16 @@ AttnKernel pick_kernel() {
 
 }  // namespace
 
+// Units of the last, partly filled wave that run in split form: all of them when
+// the doubled CTAs still fit the SMs (a sixteenth over is tolerated: block-causal
+// layouts always have a few near-empty units that retire at once), none otherwise
+// -- two half-length waves would take as long as the one they replace.
+extern "C" uint32_t qwcu_attn_sm100_tail_units(uint32_t units, uint32_t sm_count) {
+    if (!sm_count) return 0;
+    const uint32_t rest = units % sm_count;
+    return rest && 2 * rest <= sm_count + sm_count / 16 ? rest : 0u;
+}
+
 extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (a->batch == 0 || a->batch > 8 || !a->q_rows || !a->kv_rows || !a->heads || !a->kv_heads)
@@ -1310,10 +1320,10 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     if (units > 0x3fffffffull) return (int)cudaErrorInvalidValue;
     p.n_qblocks = (a->q_rows + 2 * kTileM - 1) / (2 * kTileM);
     p.total_units = (uint32_t)units;
-    const uint32_t sms = (uint32_t)sm_count_of_current_device();
-    const uint32_t rest = p.total_units % sms;
-    p.tail_units = (!a->whole_units && !whole_units_forced() && rest && 2 * rest <= sms + sms / 16)
-                       ? rest : 0u;
+    p.tail_units = (a->whole_units || whole_units_forced())
+                       ? 0u
+                       : qwcu_attn_sm100_tail_units(p.total_units,
+                                                    (uint32_t)sm_count_of_current_device());
     const unsigned grid = p.total_units + p.tail_units;
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, maps_out, p);
     rc = (int)cudaGetLastError();

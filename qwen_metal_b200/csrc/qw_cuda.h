@@ -74,6 +74,9 @@ typedef struct {
 
 /* tcgen05/TMEM/TMA flash-attention forward (sm_100a). */
 int qwcu_attn_sm100_launch(const qwcu_attn_args *args, qwcu_stream stream);
+/* How many of `units` (batch x heads x 256-row blocks) the sm100 launch runs in
+ * split form on a device with sm_count SMs (host-side arithmetic only). */
+uint32_t qwcu_attn_sm100_tail_units(uint32_t units, uint32_t sm_count);
 /* One-warp-per-(row, head) fp32 kernel; the diagnostic cross-check path. */
 int qwcu_attn_scalar_launch(const qwcu_attn_args *args, qwcu_stream stream);
 

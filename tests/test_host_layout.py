@@ -68,3 +68,24 @@ def test_workload_tables_shape():
     # the second image block sits one max(gh, gw) further along the frame axis
     assert np.isclose(cos[256, 0], np.cos(256.0), atol=1e-6)
     assert np.isclose(cos[256 + 4096, 0], np.cos(256.0 + 64.0), atol=1e-6)
+
+
+def test_split_tail_rule():
+    """Which units of an attention launch run as two half CTAs (host arithmetic of
+    the launcher): the remainder of units / SMs when doubling it still fits the SMs."""
+    import ctypes as C
+    lib = abi.load()
+    fn = lib.qwcu_attn_sm100_tail_units
+    fn.restype, fn.argtypes = C.c_uint32, [C.c_uint32, C.c_uint32]
+    sms = 148
+    assert fn(816, sms) == 76       # cfg3: 2 x 24 heads x 17 blocks -> 5 waves + 76
+    assert fn(792, sms) == 52       # cfg4: 24 heads x 33 blocks
+    assert fn(3168, sms) == 60      # cfg5
+    assert fn(102, sms) == 0        # cfg3 on one of eight GPUs: 204 halves would not fit
+    assert fn(204, sms) == 56       # ... on one of four
+    assert fn(148 * 7, sms) == 0    # full waves only
+    assert fn(48, sms) == 48        # fewer units than SMs: every unit is split
+    assert fn(10, 0) == 0
+    for units in range(1, 2000):
+        tail = fn(units, sms)
+        assert tail in (0, units % sms) and 2 * tail <= sms + sms // 16
