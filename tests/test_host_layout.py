@@ -89,3 +89,25 @@ def test_split_tail_rule():
     for units in range(1, 2000):
         tail = fn(units, sms)
         assert tail in (0, units % sms) and 2 * tail <= sms + sms // 16
+
+
+def test_prefix_limits_random_layouts_and_mask_semantics():
+    """Seeded random run layouts: the library's limits equal the oracle's bit for bit,
+    and they mean what the reference's mask means (qwen_dit.m:1651-1665): a text row
+    sees the keys up to and including itself, an image row every key up to the end of
+    its own run, and limits never decrease along the joint sequence."""
+    rng = np.random.default_rng(2024)
+    for _ in range(200):
+        runs = [(int(rng.integers(0, 40)), int(rng.integers(0, 2))) for _ in range(int(rng.integers(1, 7)))]
+        if sum(r for r, _ in runs) == 0:
+            continue
+        got = abi.prefix_limits(runs)
+        assert np.array_equal(got, O.prefix_limits(runs))
+        start = 0
+        for rows, is_image in runs:
+            for r in range(start, start + rows):
+                assert got[r] == (start + rows if is_image else r + 1)
+            start += rows
+        assert np.all(np.diff(got.astype(np.int64)) >= 0)
+        mask = O.dense_mask(got, 1, start, start)[0]
+        assert np.array_equal(mask.sum(-1), got)   # row r sees exactly the first limit[r] keys
