@@ -325,16 +325,30 @@ def run_product(args):
     tl = abi._ptr(runner.text_len) if runner.text_len is not None else None
 
     def attention_only():
+        # the same entry point the step uses, on every layer's own raw q, k (N(0,1) rows:
+        # norms of about sqrt(128), inside or within a few percent of the bound the
+        # prologue left behind, which guards against overflow by a factor 2^60)
         for (qt, kt, vt, _, _) in layers:
-            gpu.check(lib.qw_gpu_attn_block_causal_bf16(
-                gpu.handle, out_local, qt, kt, vt, runner.limits, w.batch, w.rows, heads_local,
-                heads_local, 128, tl, w.text_pad, workloads.SCALE), "attention")
+            if runner.bounded:
+                gpu.check(lib.qw_gpu_attn_block_causal_bounded_bf16(
+                    gpu.handle, out_local, qt, kt, vt, runner.limits, runner.bound, w.batch,
+                    w.rows, heads_local, heads_local, 128, tl, w.text_pad, workloads.SCALE),
+                    "attention")
+            else:
+                gpu.check(lib.qw_gpu_attn_block_causal_bf16(
+                    gpu.handle, out_local, qt, kt, vt, runner.limits, w.batch, w.rows,
+                    heads_local, heads_local, 128, tl, w.text_pad, workloads.SCALE), "attention")
 
     def prologue_only():
         for (qt, kt, vt, wqt, wkt) in layers:
-            gpu.check(lib.qw_gpu_qk_norm_rope_out_bf16(
-                gpu.handle, q_work, k_work, qt, kt, wqt, wkt, runner.cos, runner.sin, w.batch,
-                w.rows, heads_local, 128, workloads.EPS), "prologue")
+            if runner.bounded:
+                gpu.check(lib.qw_gpu_qk_norm_rope_bound_bf16(
+                    gpu.handle, q_work, k_work, qt, kt, wqt, wkt, runner.cos, runner.sin,
+                    runner.bound, w.batch, w.rows, heads_local, 128, workloads.EPS), "prologue")
+            else:
+                gpu.check(lib.qw_gpu_qk_norm_rope_out_bf16(
+                    gpu.handle, q_work, k_work, qt, kt, wqt, wkt, runner.cos, runner.sin, w.batch,
+                    w.rows, heads_local, 128, workloads.EPS), "prologue")
 
     wall0 = time.time()
     attn_s = timed(attention_only, args.steps) / (args.steps * w.layers)

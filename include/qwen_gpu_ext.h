@@ -97,6 +97,21 @@ int qw_gpu_qk_norm_rope_out_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
                                  uint32_t batch, uint32_t sequence, uint32_t heads,
                                  uint32_t head_dim, float epsilon);
 
+/* Same pass, which also writes two floats into score_bound (F32 tensor, >= 2
+ * elements): upper bounds of the 2-norm of every output query row and of every
+ * output key row (sqrt(128) * max|weight| plus rounding slack; the rotation
+ * preserves the norm).  Hand them to qw_gpu_attn_block_causal_bounded_bf16.
+ * epsilon must be >= 0. */
+int qw_gpu_qk_norm_rope_bound_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
+                                   h3_gpu_tensor *key_output, const h3_gpu_tensor *query_input,
+                                   const h3_gpu_tensor *key_input,
+                                   const h3_gpu_tensor *norm_weight_q,
+                                   const h3_gpu_tensor *norm_weight_k,
+                                   const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                   h3_gpu_tensor *score_bound, uint32_t batch,
+                                   uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                                   float epsilon);
+
 /* NEW: the prologue of a target-only layer of the edit path, where only the
  * target image rows are recomputed against the per-layer K/V cache of an
  * earlier full pass (reference qwen_dit.m:1872-1904 runs two head norms, the
@@ -130,6 +145,25 @@ int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
                                   uint32_t batch, uint32_t rows, uint32_t heads,
                                   uint32_t kv_heads, uint32_t head_dim,
                                   const uint32_t *text_len, uint32_t text_pad, float scale);
+
+/* The same op for inputs whose row norms are bounded, which is what the DiT
+ * block's QK-norm guarantees.  score_bound (F32 tensor, two elements on the
+ * device, e.g. from qw_gpu_qk_norm_rope_bound_bf16) is the caller's promise that
+ * every query row has a 2-norm <= score_bound[0] and every key row <=
+ * score_bound[1].  Then |q.k| * scale cannot exceed their product, and the kernel
+ * computes P = exp2(score - bound) against that one fixed exponent: no running
+ * row maximum, no rescaling of the accumulator.  The result is the same softmax
+ * (a common factor cancels in O / l).  A product above 60 (log2 units), or a
+ * non-finite one, is ignored and the running-maximum path runs instead; a bound
+ * that the data violates by more than 2^60 can overflow the row sums. */
+int qw_gpu_attn_block_causal_bounded_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                          const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                          const h3_gpu_tensor *value,
+                                          const h3_gpu_tensor *kv_limit,
+                                          const h3_gpu_tensor *score_bound, uint32_t batch,
+                                          uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                                          uint32_t head_dim, const uint32_t *text_len,
+                                          uint32_t text_pad, float scale);
 
 /* Context bound to an explicit CUDA device. */
 h3_gpu *qw_gpu_create_on_device(int device, char *error, size_t error_size);

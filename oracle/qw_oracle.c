@@ -258,6 +258,19 @@ void qwo_qk_rope_bf16(uint16_t *q_out, uint16_t *k_out, const uint16_t *q_in,
 }
 
 /* h3_shaders.metal:4767-4813 */
+/* The shader's threadgroup reduction: lane t of QWO_NORM_LANES sums columns t,
+ * t + lanes, ... serially, then the lanes are folded in halves (stride lanes/2,
+ * lanes/4, ..., 1).  The reference dispatches one threadgroup of 256 threads per
+ * row (h3_gpu.m:357-378: the largest power of two <= min(256, pipeline
+ * maximum)). */
+#define QWO_NORM_LANES 256
+
+static float norm_tree(float *lanes) {
+    for (uint32_t stride = QWO_NORM_LANES / 2; stride; stride >>= 1)
+        for (uint32_t t = 0; t < stride; t++) lanes[t] += lanes[t + stride];
+    return lanes[0];
+}
+
 void qwo_layer_norm_mod_bf16(uint16_t *out, const uint16_t *in,
                              const uint16_t *modulation, const uint32_t *row_map,
                              uint32_t rows, uint32_t width, uint32_t slots,
@@ -265,15 +278,22 @@ void qwo_layer_norm_mod_bf16(uint16_t *out, const uint16_t *in,
 #pragma omp parallel for schedule(static)
     for (int64_t row = 0; row < (int64_t)rows; row++) {
         const uint16_t *x = in + (size_t)row * width;
-        float sum = 0.0f;
-        for (uint32_t c = 0; c < width; c++) sum += qwo_bf16_to_f32(x[c]);
-        float mean = sum / (float)width;
-        float square = 0.0f;
-        for (uint32_t c = 0; c < width; c++) {
-            float centered = qwo_bf16_to_f32(x[c]) - mean;
-            square = fmaf(centered, centered, square);
+        float lanes[QWO_NORM_LANES];
+        for (uint32_t t = 0; t < QWO_NORM_LANES; t++) {
+            float local_sum = 0.0f;
+            for (uint32_t c = t; c < width; c += QWO_NORM_LANES) local_sum += qwo_bf16_to_f32(x[c]);
+            lanes[t] = local_sum;
         }
-        float inverse = 1.0f / sqrtf(square / (float)width + epsilon);
+        float mean = norm_tree(lanes) / (float)width;
+        for (uint32_t t = 0; t < QWO_NORM_LANES; t++) {
+            float local_square = 0.0f;
+            for (uint32_t c = t; c < width; c += QWO_NORM_LANES) {
+                float centered = qwo_bf16_to_f32(x[c]) - mean;
+                local_square = fmaf(centered, centered, local_square);
+            }
+            lanes[t] = local_square;
+        }
+        float inverse = 1.0f / sqrtf(norm_tree(lanes) / (float)width + epsilon);
         const uint16_t *scale =
             modulation + ((size_t)row_map[row] * slots + scale_slot) * width;
         for (uint32_t c = 0; c < width; c++) {

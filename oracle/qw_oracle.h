@@ -117,8 +117,9 @@ uint64_t qwo_visible_pairs(const uint32_t *kv_limit, int per_batch_limits,
 /* Affine-free LayerNorm over `width` bf16 values per row, then the per-row
  * modulation scale: out = bf16((x - mean) * rsqrt(var + eps) * (1 + scale)),
  * scale = modulation[row_map[row]][scale_slot][column], two-pass variance with
- * an fma sum of squares, all fp32 (h3_shaders.metal:4767-4813; the shader's
- * 256-way tree sum is restated as a serial sum). */
+ * an fma sum of squares, all fp32, summed in the order of the shader's 256-thread
+ * threadgroup: strided partial sums per thread, then a halving tree
+ * (h3_shaders.metal:4767-4813, dispatch h3_gpu.m:357-378). */
 void qwo_layer_norm_mod_bf16(uint16_t *out, const uint16_t *in,
                              const uint16_t *modulation, const uint32_t *row_map,
                              uint32_t rows, uint32_t width, uint32_t slots,

@@ -103,6 +103,12 @@ _SIGNATURES = {
     "qw_gpu_qk_norm_rope_out_bf16": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor,
                   c_tensor, u32, u32, u32, u32, f32]),
+    "qw_gpu_qk_norm_rope_bound_bf16": (
+        C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor,
+                  c_tensor, c_tensor, u32, u32, u32, u32, f32]),
+    "qw_gpu_attn_block_causal_bounded_bf16": (
+        C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32,
+                  u32, u32, C.c_void_p, u32, f32]),
     "qw_gpu_qk_norm_rope_cache_bf16": (
         C.c_int, [c_gpu] + [c_tensor] * 9 + [u32, u32, u32, u32, u32, f32]),
     "qw_gpu_attn_block_causal_bf16": (

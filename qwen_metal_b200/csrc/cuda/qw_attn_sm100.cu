@@ -126,6 +126,11 @@ struct KernelParams {
     uint32_t text_len[8];
     uint32_t text_pad;
     float scale_log2;  // scale * log2(e)
+    // Optional promise by the caller (two floats in device memory): every query row
+    // has a 2-norm of at most score_bound[0] and every key row of at most
+    // score_bound[1], so |q.k| <= their product and the softmax can use one fixed
+    // reference exponent instead of a running row maximum.
+    const float *score_bound;
     int head_major_out;
     // Sharded runs: the same rows are stored into every rank's full output
     // (peer-mapped pointers, plain stores over NVLink).  out_heads_total is the
@@ -311,6 +316,20 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_
           "r"((r)[11]), "r"((r)[12]), "r"((r)[13]), "r"((r)[14]), "r"((r)[15])                  \
         : "memory")
 
+// tcgen05.wait::ld that names the 32 registers of an earlier load as read-write
+// operands: no use of them can be scheduled ahead of the wait.
+#define QW_TMEM_WAIT_LD32(r)                                                                    \
+    asm volatile(                                                                               \
+        "tcgen05.wait::ld.sync.aligned;"                                                        \
+        : "+r"((r)[0]), "+r"((r)[1]), "+r"((r)[2]), "+r"((r)[3]), "+r"((r)[4]), "+r"((r)[5]),   \
+          "+r"((r)[6]), "+r"((r)[7]), "+r"((r)[8]), "+r"((r)[9]), "+r"((r)[10]), "+r"((r)[11]), \
+          "+r"((r)[12]), "+r"((r)[13]), "+r"((r)[14]), "+r"((r)[15]), "+r"((r)[16]),            \
+          "+r"((r)[17]), "+r"((r)[18]), "+r"((r)[19]), "+r"((r)[20]), "+r"((r)[21]),            \
+          "+r"((r)[22]), "+r"((r)[23]), "+r"((r)[24]), "+r"((r)[25]), "+r"((r)[26]),            \
+          "+r"((r)[27]), "+r"((r)[28]), "+r"((r)[29]), "+r"((r)[30]), "+r"((r)[31])             \
+        :                                                                                       \
+        : "memory")
+
 __device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -427,11 +446,16 @@ __device__ __forceinline__ int visited_tiles(int tiles, int lo, int hi) {
 // ---------------------------------------------------------------------------
 // Softmax + epilogue role: 128 threads per sub-tile, one query row each.
 // ---------------------------------------------------------------------------
-template <int kPoly>
+// kBounded: the caller promised |score * scale * log2(e)| <= bound (see
+// KernelParams::score_bound), so P = exp2(score*c - bound) needs no row maximum:
+// the scores stream out of TMEM 32 columns at a time, each chunk's exponentials
+// run under the next chunk's load, and O is never rescaled.
+template <int kPoly, bool kBounded>
 __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedControl *ctl,
                                              const OutMaps &maps_out, uint8_t *stage, int sub,
                                              int tid_in_group, int my_limit, uint32_t b, uint32_t h,
-                                             uint32_t row, uint32_t tile_row0, bool split) {
+                                             uint32_t row, uint32_t tile_row0, bool split,
+                                             float bound) {
     const int warp_in_group = tid_in_group >> 5;
     const uint32_t lane_base = (uint32_t)(warp_in_group * 32) << 16;
     const uint32_t tmem = ctl->tmem_base;
@@ -453,6 +477,65 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     int processed = 0;
 
     const int u_first = ctl->tile_first[sub], u_end = u_first + ctl->tile_count[sub];
+    if constexpr (kBounded) {
+        const float2 cs2 = make_float2(c, c), bias2 = make_float2(-bound, -bound);
+        float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+        for (int u = u_first; u < u_end && ok; ++u) {
+            const int j = phys_tile(ctl, u);
+            ok = mbar_wait(ctl, bar_s, phase, p.status, (1u << 16) | (uint32_t)(kBarSFull + sub),
+                           (uint32_t)j);
+            if (!ok) break;
+            phase ^= 1u;
+            tc_fence_after();
+            if (tid_in_group == 0) QW_TRACE(sub, 0, j);
+            const int key0 = j * kTileN;
+            const bool pad_hit = pad_hi > pad_lo && key0 < pad_hi && key0 + kTileN > pad_lo;
+            const bool boundary = __any_sync(0xffffffffu, key0 + kTileN > my_limit) || pad_hit;
+            uint32_t sa[32], sb[32];
+            QW_TMEM_LD32(tmem_s, sa);
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                uint32_t(&cur)[32] = (chunk & 1) ? sb : sa;
+                uint32_t(&nxt)[32] = (chunk & 1) ? sa : sb;
+                QW_TMEM_WAIT_LD32(cur);
+                if (chunk < 3) QW_TMEM_LD32(tmem_s + 32 * (chunk + 1), nxt);
+                if (boundary) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + chunk * 32 + i;
+                        const bool visible = key < my_limit && !(key >= pad_lo && key < pad_hi);
+                        cur[i] = visible ? cur[i] : __float_as_uint(-INFINITY);
+                    }
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float2 x = ffma2(make_float2(__uint_as_float(cur[2 * i]),
+                                                 __uint_as_float(cur[2 * i + 1])),
+                                     cs2, bias2);
+                    float2 pr;
+                    if ((i & 3) < kPoly) {
+                        pr = exp2_poly2(x);
+                    } else {
+                        pr.x = fast_exp2(x.x);
+                        pr.y = fast_exp2(x.y);
+                    }
+                    if (i & 1) sum_b = fadd2(sum_b, pr);
+                    else sum_a = fadd2(sum_a, pr);
+                    pk[i] = pack_bf16(pr.x, pr.y);
+                }
+                // P chunk c lands on columns [16c, 16c+16): scores already consumed.
+                QW_TMEM_ST16(tmem_s + chunk * 16, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            if ((tid_in_group & 31) == 0) mbar_arrive(bar_p);
+            if (tid_in_group == 0) QW_TRACE(sub, 4, j);
+            ++processed;
+        }
+        sum_a = fadd2(sum_a, sum_b);
+        l_run = sum_a.x + sum_a.y;
+    } else
     for (int u = u_first; u < u_end && ok; ++u) {
         const int j = phys_tile(ctl, u);
         ok = mbar_wait(ctl, bar_s, phase, p.status, (1u << 16) | (uint32_t)(kBarSFull + sub),
@@ -590,7 +673,9 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     float w_own = 1.0f, w_other = 0.0f, inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
     bool use_own = processed > 0, use_other = false;
     if (split) {
-        const float m_own = (processed > 0 && m_ref != -INFINITY) ? m_ref * fabsf(c) : -INFINITY;
+        const float m_own = kBounded ? (processed > 0 ? bound : -INFINITY)
+                            : (processed > 0 && m_ref != -INFINITY) ? m_ref * fabsf(c)
+                                                                    : -INFINITY;
         if (sub == 1) {
             // Publish exponent and row sum; warpgroup 0 reads O_1 itself (same lanes).
             ctl->merge_m[tid_in_group] = m_own;
@@ -977,7 +1062,7 @@ __device__ __forceinline__ void issue_q_loads(const KernelParams &p, SharedContr
     }
 }
 
-template <int kPoly>
+template <int kPoly, bool kMayBound>
 __global__ void __launch_bounds__(kThreads, 1)
 qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
                      const __grid_constant__ CUtensorMap map_k,
@@ -1059,7 +1144,16 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     int my_limit = 0;
     uint32_t my_row = 0;
     int sub = 0, tid_in_group = 0;
+    // Fixed reference exponent (log2 units, an integer so that P is the exact
+    // power-of-two multiple of what any other reference would give), or < 0 for
+    // the running-maximum softmax: no promise given, or one too loose to keep
+    // exp2(score*c - bound) >= 2^-2*bound inside the normal fp32 range.
+    float bound = -1.0f;
     if (tid < kSoftmaxThreads) {
+        if (kMayBound && p.score_bound) {
+            const float limit = ceilf(p.score_bound[0] * p.score_bound[1] * p.scale_log2);
+            if (limit >= 0.0f && limit <= 60.0f) bound = limit;
+        }
         sub = tid >> 7;
         tid_in_group = tid & 127;
         // (split form: both warpgroups work on the same 128 rows)
@@ -1094,9 +1188,14 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
 
     if (tid < kSoftmaxThreads) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-        softmax_role<kPoly>(p, ctl, maps_out, smem_q + (size_t)sub * kTileBytes, sub, tid_in_group,
-                            my_limit, b, h, my_row, split ? row0 : row0 + (uint32_t)sub * kTileM,
-                            split);
+        uint8_t *stage = smem_q + (size_t)sub * kTileBytes;
+        const uint32_t tile_row0 = split ? row0 : row0 + (uint32_t)sub * kTileM;
+        if (kMayBound && bound >= 0.0f)
+            softmax_role<kPoly, kMayBound>(p, ctl, maps_out, stage, sub, tid_in_group, my_limit, b,
+                                           h, my_row, tile_row0, split, bound);
+        else
+            softmax_role<kPoly, false>(p, ctl, maps_out, stage, sub, tid_in_group, my_limit, b, h,
+                                       my_row, tile_row0, split, 0.0f);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
     }
@@ -1223,25 +1322,32 @@ bool whole_units_forced() {
     return forced != 0;
 }
 
-// How many of every 4 score pairs take the polynomial exp2 (QW_CUDA_EXP_POLY=0..4
-// overrides the default for tuning).
-AttnKernel pick_kernel() {
-    static AttnKernel chosen = nullptr;
-    if (!chosen) {
-        int poly = 0;
+// The kernel variants: how many of every 4 score pairs take the polynomial exp2
+// (QW_CUDA_EXP_POLY=0..2 overrides the default for tuning), with or without the
+// fixed-exponent softmax for callers that pass a score bound.  The opt-in to
+// ~197 KB of dynamic shared memory is a per-device attribute: it is set on first
+// use on every device a process drives.
+AttnKernel pick_kernel(bool may_bound) {
+    static int poly = -1;
+    static bool ready[64][2];
+    if (poly < 0) {
         const char *env = getenv("QW_CUDA_EXP_POLY");
-        if (env && env[0] >= '0' && env[0] <= '4' && !env[1]) poly = env[0] - '0';
-        switch (poly) {
-            case 0: chosen = qw_attn_sm100_kernel<0>; break;
-            case 1: chosen = qw_attn_sm100_kernel<1>; break;
-            case 3: chosen = qw_attn_sm100_kernel<3>; break;
-            case 4: chosen = qw_attn_sm100_kernel<4>; break;
-            default: chosen = qw_attn_sm100_kernel<2>; break;
-        }
+        poly = (env && env[0] >= '0' && env[0] <= '2' && !env[1]) ? env[0] - '0' : 0;
+    }
+    AttnKernel table[3][2] = {
+        {qw_attn_sm100_kernel<0, false>, qw_attn_sm100_kernel<0, true>},
+        {qw_attn_sm100_kernel<1, false>, qw_attn_sm100_kernel<1, true>},
+        {qw_attn_sm100_kernel<2, false>, qw_attn_sm100_kernel<2, true>},
+    };
+    AttnKernel chosen = table[poly][may_bound ? 1 : 0];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    const bool tracked = dev >= 0 && dev < 64;
+    if (!tracked || !ready[dev][may_bound ? 1 : 0]) {
         if (cudaFuncSetAttribute(chosen, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemBytes) != cudaSuccess) {
-            chosen = nullptr;
-        }
+                                 (int)kSmemBytes) != cudaSuccess)
+            return nullptr;
+        if (tracked) ready[dev][may_bound ? 1 : 0] = true;
     }
     return chosen;
 }
@@ -1265,7 +1371,7 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     // TMA needs 16-byte aligned bases; cudaMalloc gives 256.
     if (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->out) & 15u)
         return (int)cudaErrorMisalignedAddress;
-    AttnKernel kernel = pick_kernel();
+    AttnKernel kernel = pick_kernel(a->score_bound != nullptr);
     if (!kernel) return (int)cudaGetLastError();
     CUtensorMap map_q, map_k, map_v;
     int rc;
@@ -1290,6 +1396,7 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     for (int i = 0; i < 8; ++i) p.text_len[i] = a->text_len[i];
     p.text_pad = a->text_pad;
     p.scale_log2 = a->scale * 1.4426950408889634f;
+    p.score_bound = a->score_bound;
     p.head_major_out = a->head_major_out;
     if (a->n_out_peers > 0) {
         if (a->n_out_peers > 8 || a->head_major_out) return (int)cudaErrorInvalidValue;

@@ -53,6 +53,7 @@ struct Params {
     int double_round;
     uint32_t strips;  // rows * tensors: one half-warp walks the heads of one (row, tensor)
     int tensors;
+    float *bound_out;  // optional: [0], [1] = upper bounds of the 2-norm of any q row, k row
 };
 
 // Two floats -> packed bf16 pair, round to nearest even in one instruction
@@ -94,6 +95,19 @@ __global__ void __launch_bounds__(256) qw_prologue_kernel(const Params p) {
             const uint4 wv = w[lane16];
             wf[0] = bf16_lo(wv.x); wf[1] = bf16_hi(wv.x); wf[2] = bf16_lo(wv.y); wf[3] = bf16_hi(wv.y);
             wf[4] = bf16_lo(wv.z); wf[5] = bf16_hi(wv.z); wf[6] = bf16_lo(wv.w); wf[7] = bf16_hi(wv.w);
+        }
+        if (p.bound_out && strip < 2u && w) {
+            // The first two strips are row 0 of q and of k.  A normalised head has
+            // sum (x*inv)^2 <= 128, so after the weight its 2-norm is at most
+            // sqrt(128) * max|w|; the two bf16 roundings (norm, rotation) and the
+            // f32 tables add well under 1 %.  The rotation itself preserves it.
+            float wmax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wmax = fmaxf(wmax, fabsf(wf[i]));
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1)
+                wmax = fmaxf(wmax, __shfl_xor_sync(half_mask, wmax, off, 16));
+            if (lane16 == 0) p.bound_out[which] = 11.313708499f * 1.01f * wmax;
         }
         if (rotate) {
             const size_t t = (size_t)((live ? row : 0u) % p.table_rows) * 16 + lane16;
@@ -196,6 +210,9 @@ extern "C" int qwcu_prologue_launch(const qwcu_prologue_args *a, qwcu_stream str
     p.double_round = a->double_round;
     p.v_in = static_cast<const uint4 *>(a->v_in);
     p.v_out = static_cast<uint4 *>(a->v_out);
+    p.bound_out = a->bound_out;
+    if (a->bound_out && (!a->k_in || a->v_in || !a->norm_weight_q || !a->norm_weight_k))
+        return (int)cudaErrorInvalidValue;
     if (a->v_in && (!a->k_in || !a->v_out)) return (int)cudaErrorInvalidValue;
     p.tensors = a->v_in ? 3 : a->k_in ? 2 : 1;
     unsigned long long strips = (unsigned long long)a->rows * p.tensors;

@@ -58,6 +58,11 @@ typedef struct {
     uint32_t text_pad;
     float scale;
     int scale_in_q; /* h3 causal variant: q' = bf16(q*scale), scores unscaled */
+    /* Optional (sm100 kernel): two device floats, upper bounds of the 2-norm of
+     * every query row and of every key row.  When their product times
+     * scale*log2(e) is at most 60 the softmax uses that as one fixed reference
+     * exponent (no row maximum, no rescaling); otherwise it is ignored. */
+    const float *score_bound;
     int head_major_out;
     /* Sharded heads (n_out_peers > 0, sm100 kernel only): instead of `out`, the
      * rows are stored at head columns [out_head_offset, out_head_offset + heads)
@@ -105,6 +110,10 @@ typedef struct {
     uint32_t heads;
     float epsilon;
     int double_round;
+    /* Optional (q and k both normed, no third tensor): two device floats that
+     * receive upper bounds of the 2-norm of any output q row and k row,
+     * sqrt(128) * max|weight| plus rounding slack. */
+    float *bound_out;
 } qwcu_prologue_args;
 
 int qwcu_prologue_launch(const qwcu_prologue_args *args, qwcu_stream stream);

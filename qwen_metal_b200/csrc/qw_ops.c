@@ -150,15 +150,20 @@ int qw_gpu_qk_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output, h3_gpu_tensor 
 }
 
 /* NEW: fused norm(q), norm(k), rope(q, k) (reference sequence qwen_dit.m:1273-1278) */
-int qw_gpu_qk_norm_rope_out_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
-                                 h3_gpu_tensor *key_output, const h3_gpu_tensor *query_input,
-                                 const h3_gpu_tensor *key_input,
-                                 const h3_gpu_tensor *norm_weight_q,
-                                 const h3_gpu_tensor *norm_weight_k,
-                                 const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
-                                 uint32_t batch, uint32_t sequence, uint32_t heads,
-                                 uint32_t head_dim, float epsilon) {
+static int qk_norm_rope(h3_gpu *gpu, h3_gpu_tensor *query_output, h3_gpu_tensor *key_output,
+                        const h3_gpu_tensor *query_input, const h3_gpu_tensor *key_input,
+                        const h3_gpu_tensor *norm_weight_q, const h3_gpu_tensor *norm_weight_k,
+                        const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                        h3_gpu_tensor *score_bound, int want_bound, uint32_t batch,
+                        uint32_t sequence, uint32_t heads, uint32_t head_dim, float epsilon) {
     if (!gpu) return 0;
+    if (want_bound) {
+        if (!qw_require_dtype(gpu, score_bound, 2, H3_GPU_F32, "QK norm+rope score bound")) return 0;
+        if (!(epsilon >= 0.0f)) {
+            qw_set_error(gpu, "QK norm+rope: the score bound needs epsilon >= 0");
+            return 0;
+        }
+    }
     size_t count = (size_t)batch * sequence * heads * head_dim;
     size_t rope_count = (size_t)sequence * (head_dim / 2);
     if (!qw_require_dtype(gpu, query_input, count, H3_GPU_BF16, "QK norm+rope query") ||
@@ -193,7 +198,37 @@ int qw_gpu_qk_norm_rope_out_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
     args.table_rows = sequence;
     args.heads = heads;
     args.epsilon = epsilon;
+    args.bound_out = want_bound ? (float *)score_bound->dev : NULL;
     return launch_prologue(gpu, &args, "QK norm+rope");
+}
+
+int qw_gpu_qk_norm_rope_out_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
+                                 h3_gpu_tensor *key_output, const h3_gpu_tensor *query_input,
+                                 const h3_gpu_tensor *key_input,
+                                 const h3_gpu_tensor *norm_weight_q,
+                                 const h3_gpu_tensor *norm_weight_k,
+                                 const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                 uint32_t batch, uint32_t sequence, uint32_t heads,
+                                 uint32_t head_dim, float epsilon) {
+    return qk_norm_rope(gpu, query_output, key_output, query_input, key_input, norm_weight_q,
+                        norm_weight_k, rope_cos, rope_sin, NULL, 0, batch, sequence, heads,
+                        head_dim, epsilon);
+}
+
+/* NEW: the same pass, which also leaves in score_bound[0..1] (F32 tensor) upper
+ * bounds of the 2-norm of every output query row and key row. */
+int qw_gpu_qk_norm_rope_bound_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
+                                   h3_gpu_tensor *key_output, const h3_gpu_tensor *query_input,
+                                   const h3_gpu_tensor *key_input,
+                                   const h3_gpu_tensor *norm_weight_q,
+                                   const h3_gpu_tensor *norm_weight_k,
+                                   const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                   h3_gpu_tensor *score_bound, uint32_t batch,
+                                   uint32_t sequence, uint32_t heads, uint32_t head_dim,
+                                   float epsilon) {
+    return qk_norm_rope(gpu, query_output, key_output, query_input, key_input, norm_weight_q,
+                        norm_weight_k, rope_cos, rope_sin, score_bound, 1, batch, sequence, heads,
+                        head_dim, epsilon);
 }
 
 int qw_gpu_qk_norm_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key,
@@ -592,4 +627,31 @@ int qw_gpu_attn_block_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
                                  heads, kv_heads, head_dim, text_len, text_pad, scale))
         return 0;
     return qw_launch_attention(gpu, &args, "block-causal attention");
+}
+
+/* NEW: the same op for normed inputs.  score_bound (F32 tensor, two elements, as
+ * left by qw_gpu_qk_norm_rope_bound_bf16) promises ||q row|| <= [0] and
+ * ||k row|| <= [1]; the kernel then runs the softmax against one fixed reference
+ * exponent instead of a running row maximum. */
+int qw_gpu_attn_block_causal_bounded_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
+                                          const h3_gpu_tensor *query, const h3_gpu_tensor *key,
+                                          const h3_gpu_tensor *value,
+                                          const h3_gpu_tensor *kv_limit,
+                                          const h3_gpu_tensor *score_bound, uint32_t batch,
+                                          uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                                          uint32_t head_dim, const uint32_t *text_len,
+                                          uint32_t text_pad, float scale) {
+    if (!gpu) return 0;
+    if (!output) {
+        qw_set_error(gpu, "block-causal attention output tensor is absent or too small");
+        return 0;
+    }
+    if (!qw_require_dtype(gpu, score_bound, 2, H3_GPU_F32, "block-causal attention score bound"))
+        return 0;
+    qwcu_attn_args args;
+    if (!qw_prepare_block_causal(gpu, &args, output, query, key, value, kv_limit, batch, rows,
+                                 heads, kv_heads, head_dim, text_len, text_pad, scale))
+        return 0;
+    args.score_bound = (const float *)score_bound->dev;
+    return qw_launch_attention(gpu, &args, "block-causal attention (bounded)");
 }

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 
 import numpy as np
 
@@ -140,9 +141,17 @@ def layer_inputs(w: Workload, layer: int, base_seed: int = 20261028):
 class LayerRunner:
     """Device-resident state of one workload and the per-layer op sequence."""
 
-    def __init__(self, gpu: abi.Gpu, w: Workload, heads_local: int | None = None):
+    def __init__(self, gpu: abi.Gpu, w: Workload, heads_local: int | None = None,
+                 bounded: bool | None = None):
         self.gpu, self.w = gpu, w
         self.heads = heads_local or w.heads
+        # With the QK-norm in front, the prologue also leaves the norm bounds of its
+        # outputs on the device and the attention kernel runs its fixed-exponent
+        # softmax; QW_SOFTMAX=max (or bounded=False) keeps the running-maximum path.
+        if bounded is None:
+            bounded = os.environ.get("QW_SOFTMAX", "bounded") != "max"
+        self.bounded = bool(bounded and w.prologue)
+        self.bound = gpu.new_f32(2) if self.bounded else None
         n = w.batch * w.rows * self.heads * HEAD_DIM
         self.n = n
         self.limits_host = w.limits()
@@ -163,10 +172,15 @@ class LayerRunner:
         out = out or self.out
         if w.prologue:
             qo, ko = (q_work or q), (k_work or k)
-            g.check(lib.qw_gpu_qk_norm_rope_out_bf16(g.handle, qo, ko, q, k, wq, wk, self.cos,
-                                                     self.sin, w.batch, w.rows, self.heads,
-                                                     HEAD_DIM, EPS),
-                    "qk_norm_rope")
+            if self.bounded:
+                g.check(lib.qw_gpu_qk_norm_rope_bound_bf16(
+                    g.handle, qo, ko, q, k, wq, wk, self.cos, self.sin, self.bound, w.batch,
+                    w.rows, self.heads, HEAD_DIM, EPS), "qk_norm_rope_bound")
+            else:
+                g.check(lib.qw_gpu_qk_norm_rope_out_bf16(g.handle, qo, ko, q, k, wq, wk, self.cos,
+                                                         self.sin, w.batch, w.rows, self.heads,
+                                                         HEAD_DIM, EPS),
+                        "qk_norm_rope")
             q, k = qo, ko
         tl = abi._ptr(self.text_len) if self.text_len is not None else None
         if group is not None:
@@ -174,6 +188,11 @@ class LayerRunner:
                 group, full, q, k, v, self.limits, w.batch, w.rows, self.heads, self.heads,
                 HEAD_DIM, tl, w.text_pad, SCALE), "group_attn_block_causal")
             return full
+        if self.bounded:
+            g.check(lib.qw_gpu_attn_block_causal_bounded_bf16(
+                g.handle, out, q, k, v, self.limits, self.bound, w.batch, w.rows, self.heads,
+                self.heads, HEAD_DIM, tl, w.text_pad, SCALE), "attn_block_causal_bounded")
+            return out
         g.check(lib.qw_gpu_attn_block_causal_bf16(g.handle, out, q, k, v, self.limits, w.batch,
                                                   w.rows, self.heads, self.heads, HEAD_DIM, tl,
                                                   w.text_pad, SCALE),

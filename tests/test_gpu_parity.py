@@ -198,9 +198,9 @@ def sample_rows(w, count, seed=5):
     return np.array([b * w.rows + r for b in range(w.batch) for r in per_item], np.uint32)
 
 
-def run_workload_layer(gpu, w, layer=0):
+def run_workload_layer(gpu, w, layer=0, bounded=None):
     q, k, v, wq, wk = workloads.layer_inputs(w, layer)
-    runner = workloads.LayerRunner(gpu, w)
+    runner = workloads.LayerRunner(gpu, w, bounded=bounded)
     qt, kt, vt = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v)
     wqt, wkt = (gpu.bf16(wq), gpu.bf16(wk)) if w.prologue else (None, None)
     gpu.begin()
@@ -273,6 +273,58 @@ def test_cfg3_sm100_agrees_with_scalar_kernel_everywhere(gpu):
     gates(out_fast, bf16_to_f32(out_ref), "cfg3 sm100 vs scalar")
 
 
+def test_bounded_softmax_against_running_max_and_oracle(gpu, tail_form):
+    """The fixed-exponent softmax (score bound from the prologue) and the
+    running-maximum softmax are the same function: both meet the gates against
+    the oracle on cfg2 in full, and agree with each other within them."""
+    w = workloads.workload(2)
+    inputs, out_bounded = run_workload_layer(gpu, w, bounded=True)
+    _, out_max = run_workload_layer(gpu, w, bounded=False)
+    ref = oracle_layer(w, inputs)
+    gates(out_bounded, ref, "cfg2 bounded softmax")
+    gates(out_max, ref, "cfg2 running-max softmax")
+    gates(out_bounded, bf16_to_f32(out_max), "bounded vs running max")
+
+
+def test_score_bound_is_an_upper_bound_and_loose_bounds_fall_back(gpu):
+    """The prologue's two floats bound the row norms of what it wrote; a bound too
+    loose for the fixed exponent (product * scale * log2(e) > 60) makes the kernel
+    take the running-maximum path, with the same result."""
+    rng = np.random.default_rng(77)
+    S, H = 300, 4
+    lib = gpu.lib
+    cos, sin = abi.rope_tables(44, 16, 16)
+    limits = O.prefix_limits([(44, 0), (256, 1)])
+    for weight_scale in (1.0, 4.0):  # 4.0: bound product ~ (11.4*4.6)^2 * 0.1275 >> 60
+        q, k, v = (randn_bf16(rng, (1, S, H, 128)) for _ in range(3))
+        wq = randn_bf16(rng, (128,), weight_scale, 0.1)
+        wk = randn_bf16(rng, (128,), weight_scale, 0.1)
+        qt, kt, vt, wqt, wkt = (gpu.bf16(x) for x in (q, k, v, wq, wk))
+        ct, st, lt = gpu.f32(cos), gpu.f32(sin), gpu.u32(limits)
+        bt, ot = gpu.new_f32(2), gpu.new_bf16(q.size)
+        gpu.begin()
+        gpu.check(lib.qw_gpu_qk_norm_rope_bound_bf16(gpu.handle, qt, kt, qt, kt, wqt, wkt, ct, st,
+                                                     bt, 1, S, H, 128, 1e-6), "prologue")
+        gpu.check(lib.qw_gpu_attn_block_causal_bounded_bf16(
+            gpu.handle, ot, qt, kt, vt, lt, bt, 1, S, H, H, 128, None, 0, SCALE), "attention")
+        gpu.submit()
+        bound = gpu.read_f32(bt, 2)
+        qn = bf16_to_f32(gpu.read_bf16(qt, q.size)).reshape(S, H, 128).astype(np.float64)
+        kn = bf16_to_f32(gpu.read_bf16(kt, k.size)).reshape(S, H, 128).astype(np.float64)
+        assert np.sqrt((qn ** 2).sum(-1)).max() <= bound[0]
+        assert np.sqrt((kn ** 2).sum(-1)).max() <= bound[1]
+        assert bound[0] <= 11.32 * 1.011 * np.abs(bf16_to_f32(wq)).max() + 1e-3
+        exponent = bound[0] * bound[1] * SCALE * 1.4426950408889634
+        assert (exponent <= 60) == (weight_scale == 1.0)
+        rq, rk = prologue_oracle(q, k, wq, wk, cos, sin, 1, S, H)
+        ref, _ = O.sdpa(rq, rk, v, limits, 1, S, S, H, H, SCALE)
+        # the larger weights sharpen the softmax; the gates still hold (the oracle
+        # sees the same normed inputs)
+        gates(gpu.read_bf16(ot, q.size), ref, f"bounded entry point, weights ~{weight_scale}")
+        for t in (qt, kt, vt, wqt, wkt, ct, st, lt, bt, ot):
+            gpu.free(t)
+
+
 # --------------------------------------------------------------------------
 # integer mask indexing, bit-exact on the device
 # --------------------------------------------------------------------------
@@ -294,9 +346,11 @@ def test_split_blocks_agree_with_whole_blocks(gpu):
     gates(first, bf16_to_f32(whole), "split vs whole blocks")
 
 
+@pytest.mark.parametrize("softmax", ["max", "bounded"])
 @pytest.mark.parametrize("case", ["kat", "cfg3", "ragged"])
-def test_mask_indexing_bit_exact(gpu, tail_form, case):
-    """q = 0 makes every visible key weigh exactly 1, V[s, d] = [s % 128 == d]
+def test_mask_indexing_bit_exact(gpu, tail_form, case, softmax):
+    """q = 0 makes every visible key weigh exactly 1 (2^-bound with the fixed
+    reference exponent, which cancels exactly), V[s, d] = [s % 128 == d]
     makes O[r, d] the count of visible keys in residue class d: the output is
     bf16(count_d * (1 / count)), reproducible exactly from the oracle's dense mask."""
     if case == "kat":
@@ -316,10 +370,19 @@ def test_mask_indexing_bit_exact(gpu, tail_form, case):
     lib = gpu.lib
     qt, kt, vt, lt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.u32(limits), gpu.new_bf16(q.size)
     gpu.begin()
-    gpu.check(lib.qw_gpu_attn_block_causal_bf16(
-        gpu.handle, ot, qt, kt, vt, lt, batch, S, H, H, 128,
-        abi._ptr(text_len) if text_len is not None else None, pad, SCALE), "mask probe")
+    tl_ptr = abi._ptr(text_len) if text_len is not None else None
+    if softmax == "bounded":
+        # q = 0 satisfies any bound; 4 * 4 * scale * log2(e) rounds up to exponent 3
+        bt = gpu.f32(np.array([4.0, 4.0], np.float32))
+        gpu.check(lib.qw_gpu_attn_block_causal_bounded_bf16(
+            gpu.handle, ot, qt, kt, vt, lt, bt, batch, S, H, H, 128, tl_ptr, pad, SCALE),
+            "mask probe (bounded)")
+    else:
+        gpu.check(lib.qw_gpu_attn_block_causal_bf16(
+            gpu.handle, ot, qt, kt, vt, lt, batch, S, H, H, 128, tl_ptr, pad, SCALE), "mask probe")
     gpu.submit()
+    if softmax == "bounded":
+        gpu.free(bt)
     got = gpu.read_bf16(ot, q.size).reshape(q.shape)
     mask = O.dense_mask(limits, batch, S, S, text_len, pad)
     onehot = np.zeros((S, 128), np.float32)
