@@ -92,8 +92,19 @@ void qw_count_launch(h3_gpu *gpu, int rc, const char *what) {
     }
 }
 
+/* Scratch of at least `bytes`, or NULL with the error set.  The block is cached in
+ * the context, so it must never be a graph-owned allocation: while a capture is
+ * active the block may be reused but neither created nor grown (an allocation
+ * captured into a graph is only backed while that graph runs). */
 void *qw_scratch(h3_gpu *gpu, size_t bytes) {
     if (gpu->scratch_bytes >= bytes) return gpu->scratch;
+    if (gpu->capturing) {
+        qw_set_error(gpu, "this op needs %zu bytes of scratch but only %zu are allocated: run it "
+                          "once at this size before capturing it into a graph",
+                     bytes, gpu->scratch_bytes);
+        gpu->chain_failed = 1;
+        return NULL;
+    }
     if (gpu->scratch) {
         /* Earlier launches may still read the old block: stream-ordered free. */
         cudaFreeAsync(gpu->scratch, gpu->stream);
@@ -103,6 +114,7 @@ void *qw_scratch(h3_gpu *gpu, size_t bytes) {
     void *block = NULL;
     if (cudaMallocAsync(&block, bytes, gpu->stream) != cudaSuccess) {
         cudaGetLastError();
+        qw_set_error(gpu, "cannot allocate %zu bytes of scratch", bytes);
         return NULL;
     }
     gpu->scratch = block;

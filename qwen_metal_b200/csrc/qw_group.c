@@ -194,6 +194,13 @@ int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
                                           cudaMemcpyDeviceToDevice, gpu->stream),
                           "head gather copy");
     if (group->staging_bytes < full_count * 2) {
+        if (gpu->capturing) {
+            qw_set_error(gpu, "head gather: the landing zone must grow to %zu bytes: run the "
+                              "gather once at this size before capturing it into a graph",
+                         full_count * 2);
+            gpu->chain_failed = 1;
+            return 0;
+        }
         if (group->staging) {
             cudaStreamSynchronize(gpu->stream);
             cudaFree(group->staging);

@@ -320,10 +320,7 @@ int qw_launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what) {
          * (h3_shaders.metal:4396-4402). */
         size_t count = (size_t)args->batch * args->q_rows * args->heads * 128;
         void *scaled = qw_scratch(gpu, count * 2);
-        if (!scaled) {
-            qw_set_error(gpu, "%s: cannot allocate %zu bytes of scratch", what, count * 2);
-            return 0;
-        }
+        if (!scaled) return 0; /* message set by qw_scratch */
         int rc = qwcu_scale_bf16_launch(scaled, args->q, count, args->scale, gpu->stream);
         qw_count_launch(gpu, rc, "query pre-scale");
         if (rc) return 0;

@@ -552,6 +552,75 @@ def test_error_conventions(gpu):
         gpu.free(x)
 
 
+def test_range_copies_move_the_bytes(gpu):
+    """h3_gpu_copy_bf16 / _f32 (reference h3_gpu.m:1384-1444; the DiT block slices Q
+    per run and scatters the attention output with them): the copied range arrives
+    bit for bit and nothing outside it changes."""
+    lib = gpu.lib
+    rng = np.random.default_rng(5)
+    src16 = rng.integers(0, 1 << 16, 1000).astype(np.uint16)
+    dst16 = np.full(1200, 0xABCD, np.uint16)
+    src32 = rng.standard_normal(1000).astype(np.float32)
+    dst32 = np.full(1200, -7.25, np.float32)
+    s16, d16, s32, d32 = gpu.bf16(src16), gpu.bf16(dst16), gpu.f32(src32), gpu.f32(dst32)
+    gpu.begin()
+    gpu.check(lib.h3_gpu_copy_bf16(gpu.handle, d16, 100, s16, 17, 800), "copy bf16")
+    gpu.check(lib.h3_gpu_copy_f32(gpu.handle, d32, 3, s32, 0, 1000), "copy f32")
+    gpu.check(lib.h3_gpu_copy_bf16(gpu.handle, d16, 1000, d16, 100, 64), "copy inside one tensor")
+    gpu.check(lib.h3_gpu_copy_bf16(gpu.handle, d16, 0, s16, 0, 0), "empty copy")
+    gpu.submit()
+    want16 = dst16.copy()
+    want16[100:900] = src16[17:817]
+    want16[1000:1064] = want16[100:164]
+    want32 = dst32.copy()
+    want32[3:1003] = src32
+    assert np.array_equal(gpu.read_bf16(d16, 1200), want16)
+    assert np.array_equal(gpu.read_f32(d32, 1200).view(np.uint32), want32.view(np.uint32))
+    assert np.array_equal(gpu.read_bf16(s16, 1000), src16)  # the source is untouched
+    for t in (s16, d16, s32, d32):
+        gpu.free(t)
+
+
+def test_scratch_cannot_grow_inside_a_graph_capture(gpu):
+    """The h3 causal op keeps its pre-scaled query in scratch that the context
+    caches.  Inside a graph capture that block may be reused but not created or
+    grown (a captured allocation is only backed while the graph runs): the op
+    refuses with a message, the chain reports the failure, and the context works
+    normally afterwards."""
+    lib = gpu.lib
+    rng = np.random.default_rng(3)
+    big, H = 4096, 8   # larger than any earlier test's use of the op
+    q, k, v = (randn_bf16(rng, (big, H, 128)) for _ in range(3))
+    qt, kt, vt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.new_bf16(q.size)
+    gpu.begin()
+    gpu.check(lib.h3_gpu_gqa_causal_bf16(gpu.handle, ot, qt, kt, vt, 64, H, H, 128, SCALE), "warm-up")
+    gpu.submit()
+    gpu.begin()
+    gpu.check(lib.qw_gpu_graph_begin(gpu.handle), "graph begin")
+    assert lib.h3_gpu_gqa_causal_bf16(gpu.handle, ot, qt, kt, vt, big, H, H, 128, SCALE) == 0
+    assert "before capturing" in gpu.error()
+    graph = lib.qw_gpu_graph_end(gpu.handle)
+    if graph:
+        lib.qw_gpu_graph_free(graph)
+    assert lib.h3_gpu_submit(gpu.handle) == 0          # the chain carries the failure
+    # the same size outside a capture allocates; a capture at that size then works
+    gpu.begin()
+    gpu.check(lib.h3_gpu_gqa_causal_bf16(gpu.handle, ot, qt, kt, vt, big, H, H, 128, SCALE), "grow")
+    gpu.submit()
+    first = gpu.read_bf16(ot, q.size)
+    gpu.begin()
+    gpu.check(lib.qw_gpu_graph_begin(gpu.handle), "graph begin")
+    gpu.check(lib.h3_gpu_gqa_causal_bf16(gpu.handle, ot, qt, kt, vt, big, H, H, 128, SCALE), "captured")
+    graph = lib.qw_gpu_graph_end(gpu.handle)
+    assert graph, gpu.error()
+    gpu.check(lib.qw_gpu_graph_launch(gpu.handle, graph), "replay")
+    gpu.submit()
+    assert np.array_equal(gpu.read_bf16(ot, q.size), first)
+    lib.qw_gpu_graph_free(graph)
+    for t in (qt, kt, vt, ot):
+        gpu.free(t)
+
+
 def test_rope_tables_on_device_match_host(gpu):
     lib = gpu.lib
     cos_t, sin_t = abi.c_tensor(), abi.c_tensor()
