@@ -46,6 +46,21 @@ __device__ __forceinline__ uint16_t round_bf16(float v) {
     return (uint16_t)(pack_bf16(v, 0.0f) & 0xffffu);
 }
 
+// The modulation row of a token: row_map[row] indexes [maps][slots][width].  An
+// index outside the tensor is recorded in the status words (the submit then
+// fails) and row 0 is used instead, so a stale map cannot read out of bounds.
+__device__ __forceinline__ uint32_t checked_map(const uint32_t *row_map, uint32_t row,
+                                                uint32_t maps, uint32_t *status) {
+    const uint32_t map = row_map[row];
+    if (map < maps) return map;
+    if (status && atomicCAS(status, 0u, (uint32_t)QWCU_STATUS_BAD_ARGUMENT) == 0u) {
+        status[1] = 0x40000u;  // where: modulation row index
+        status[2] = row;
+        status[3] = map;
+    }
+    return 0u;
+}
+
 struct NormArgs {
     const uint16_t *in;
     const uint16_t *modulation;
@@ -53,6 +68,8 @@ struct NormArgs {
     uint16_t *out;
     uint32_t rows, width, slots, scale_slot;
     float epsilon;
+    uint32_t maps;
+    uint32_t *status;
 };
 
 // width % 8 == 0 and width <= 32 * kVecs * 8.  A warp walks rows (stride = warps
@@ -73,7 +90,7 @@ qw_layer_norm_mod_kernel(const NormArgs a) {
             const uint32_t v = lane + 32u * i;
             x[i] = v < vecs ? __ldcs(src + v) : make_uint4(0, 0, 0, 0);
         }
-        const uint32_t map = a.row_map[row];
+        const uint32_t map = checked_map(a.row_map, row, a.maps, a.status);
         const uint4 *scale = reinterpret_cast<const uint4 *>(
             a.modulation + ((size_t)map * a.slots + a.scale_slot) * a.width);
 
@@ -139,7 +156,8 @@ qw_layer_norm_mod_generic_kernel(const NormArgs a) {
     }
     const float inverse = rsqrtf(warp_sum(square) / (float)a.width + a.epsilon);
     const uint16_t *scale =
-        a.modulation + ((size_t)a.row_map[row] * a.slots + a.scale_slot) * a.width;
+        a.modulation +
+        ((size_t)checked_map(a.row_map, row, a.maps, a.status) * a.slots + a.scale_slot) * a.width;
     for (uint32_t c = lane; c < a.width; c += 32) {
         const float n = __fmul_rn(__fsub_rn(__uint_as_float((uint32_t)x[c] << 16), mean), inverse);
         const float s = __uint_as_float((uint32_t)scale[c] << 16);
@@ -154,6 +172,8 @@ struct GateArgs {
     const uint32_t *row_map;
     uint16_t *out;
     uint32_t rows, width, slots, gate_slot;
+    uint32_t maps;
+    uint32_t *status;
 };
 
 // width % 8 == 0: one 16-byte vector per thread and step.
@@ -171,7 +191,8 @@ __global__ void __launch_bounds__(256) qw_gate_kernel(const GateArgs a) {
         const uint4 b = __ldcs(branch + i);
         const uint4 g = __ldg(reinterpret_cast<const uint4 *>(
                                   a.modulation +
-                                  ((size_t)a.row_map[row] * a.slots + a.gate_slot) * a.width) +
+                                  ((size_t)checked_map(a.row_map, row, a.maps, a.status) * a.slots +
+                                   a.gate_slot) * a.width) +
                               v);
         const uint32_t rw[4] = {r.x, r.y, r.z, r.w}, bw[4] = {b.x, b.y, b.z, b.w},
                        gw[4] = {g.x, g.y, g.z, g.w};
@@ -191,7 +212,8 @@ __global__ void __launch_bounds__(256) qw_gate_generic_kernel(const GateArgs a) 
         const uint32_t row = (uint32_t)(i / a.width);
         const uint32_t c = (uint32_t)(i - (size_t)row * a.width);
         const float gate = __uint_as_float(
-            (uint32_t)a.modulation[((size_t)a.row_map[row] * a.slots + a.gate_slot) * a.width + c]
+            (uint32_t)a.modulation[((size_t)checked_map(a.row_map, row, a.maps, a.status) * a.slots +
+                                    a.gate_slot) * a.width + c]
             << 16);
         const float value = __fadd_rn(__uint_as_float((uint32_t)a.residual[i] << 16),
                                       __fmul_rn(__uint_as_float((uint32_t)a.branch[i] << 16), gate));
@@ -217,6 +239,9 @@ extern "C" int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *a, int sm_cou
     k.slots = a->slots;
     k.scale_slot = a->slot;
     k.epsilon = a->epsilon;
+    k.maps = a->maps;
+    k.status = a->status;
+    if (!a->maps) return (int)cudaErrorInvalidValue;
     const unsigned blocks = (a->rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
     const bool vector = a->width % 8 == 0 && a->width <= 32u * kMaxVecs * 8u &&
                         aligned16(k.in) && aligned16(k.out) && aligned16(k.modulation);
@@ -252,6 +277,9 @@ extern "C" int qwcu_gate_launch(const qwcu_rowwise_args *a, int sm_count, qwcu_s
     k.width = a->width;
     k.slots = a->slots;
     k.gate_slot = a->slot;
+    k.maps = a->maps;
+    k.status = a->status;
+    if (!a->maps) return (int)cudaErrorInvalidValue;
     const bool vector = a->width % 8 == 0 && aligned16(k.residual) && aligned16(k.branch) &&
                         aligned16(k.out) && aligned16(k.modulation);
     const size_t items = vector ? (size_t)a->rows * (a->width / 8) : (size_t)a->rows * a->width;

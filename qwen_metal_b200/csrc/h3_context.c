@@ -452,11 +452,18 @@ int h3_gpu_submit(h3_gpu *gpu) {
     }
     if (gpu->chain_failed) return 0; /* message already set by the failing launch */
     if (gpu->status_host[0] != QWCU_STATUS_OK) {
-        qw_set_error(gpu,
-                     "CUDA kernel reported status %u (where 0x%x, tile %u, block 0x%x): a bounded "
-                     "device-side wait ran out",
-                     gpu->status_host[0], gpu->status_host[1], gpu->status_host[2],
-                     gpu->status_host[3]);
+        if (gpu->status_host[0] == QWCU_STATUS_BAD_ARGUMENT)
+            qw_set_error(gpu,
+                         "CUDA kernel reported status %u (where 0x%x): row %u carries modulation "
+                         "row index %u, outside the modulation tensor; block 0 was used instead",
+                         gpu->status_host[0], gpu->status_host[1], gpu->status_host[2],
+                         gpu->status_host[3]);
+        else
+            qw_set_error(gpu,
+                         "CUDA kernel reported status %u (where 0x%x, tile %u, block 0x%x): a "
+                         "bounded device-side wait ran out",
+                         gpu->status_host[0], gpu->status_host[1], gpu->status_host[2],
+                         gpu->status_host[3]);
         cudaMemsetAsync(gpu->status_dev, 0, QWCU_STATUS_WORDS * sizeof(uint32_t), gpu->stream);
         return 0;
     }

@@ -133,6 +133,8 @@ typedef struct {
     uint32_t slots;
     uint32_t slot;
     float epsilon; /* norm only */
+    uint32_t maps;    /* [maps][slots][width] blocks the modulation tensor holds (>= 1) */
+    uint32_t *status; /* a row_map entry >= maps is reported here; block 0 is used */
 } qwcu_rowwise_args;
 
 int qwcu_layer_norm_mod_launch(const qwcu_rowwise_args *args, int sm_count, qwcu_stream stream);

@@ -77,9 +77,16 @@ int qw_gpu_layer_norm_mod_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_
         qw_set_error(gpu, "Qwen AdaLN: empty geometry");
         return 0;
     }
+    size_t maps = modulation->elements / ((size_t)slots * width);
+    if (!maps) {
+        qw_set_error(gpu, "Qwen AdaLN: the modulation tensor holds less than one [%u, %u] block",
+                     slots, width);
+        return 0;
+    }
     if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
     qwcu_rowwise_args args = {input->dev, NULL, modulation->dev, row_map->dev, output->dev,
-                              rows, width, slots, scale_slot, epsilon};
+                              rows, width, slots, scale_slot, epsilon,
+                              maps > UINT32_MAX ? UINT32_MAX : (uint32_t)maps, gpu->status_dev};
     int rc = qwcu_layer_norm_mod_launch(&args, qwcu_device_sm_count(gpu->device), gpu->stream);
     qw_count_launch(gpu, rc, "Qwen AdaLN");
     return rc == 0;
@@ -106,9 +113,16 @@ int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *re
         qw_set_error(gpu, "gate: empty geometry");
         return 0;
     }
+    size_t maps = modulation->elements / ((size_t)slots * width);
+    if (!maps) {
+        qw_set_error(gpu, "gate: the modulation tensor holds less than one [%u, %u] block", slots,
+                     width);
+        return 0;
+    }
     if (!qw_require_command(gpu) || !qw_bind(gpu)) return 0;
     qwcu_rowwise_args args = {residual->dev, branch->dev, modulation->dev, row_map->dev,
-                              output->dev, rows, width, slots, gate_slot, 0.0f};
+                              output->dev, rows, width, slots, gate_slot, 0.0f,
+                              maps > UINT32_MAX ? UINT32_MAX : (uint32_t)maps, gpu->status_dev};
     int rc = qwcu_gate_launch(&args, qwcu_device_sm_count(gpu->device), gpu->stream);
     qw_count_launch(gpu, rc, "gate");
     return rc == 0;
@@ -573,7 +587,16 @@ int qw_prepare_block_causal(h3_gpu *gpu, qwcu_attn_args *args, h3_gpu_tensor *ou
         if (!qw_require_elements(gpu, kv_limit, rows, "block-causal attention limit") ||
             kv_limit->dtype != H3_GPU_U32)
             return 0;
-        per_batch = batch > 1 && kv_limit->elements >= (size_t)batch * rows;
+        /* One table shared by the batch (`rows` entries) or one per item
+         * (`batch * rows`): the size says which, so it must be one of the two. */
+        if (batch > 1 && kv_limit->elements != rows &&
+            kv_limit->elements != (size_t)batch * rows) {
+            qw_set_error(gpu, "block-causal attention limit tensor must hold rows (%u) or "
+                              "batch*rows (%zu) entries, not %zu",
+                         rows, (size_t)batch * rows, kv_limit->elements);
+            return 0;
+        }
+        per_batch = batch > 1 && kv_limit->elements == (size_t)batch * rows;
     }
     if (text_len && text_pad) {
         if (text_pad > rows) {

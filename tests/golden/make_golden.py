@@ -49,7 +49,8 @@ def f32(path):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--ref", default="/root/reference")
+    parser.add_argument("--ref", default=os.environ.get("QWEN_METAL_REF") or
+                        os.path.join(os.path.dirname(ROOT), "reference"))
     args = parser.parse_args()
     ref = args.ref
     if not os.path.isdir(ref):

@@ -96,6 +96,20 @@ def test_cfg0_reference_test_binary(gpu):
     assert "PASS" in res.stdout, res.stdout + res.stderr
 
 
+def test_reference_sdpa_benchmark_binary(gpu):
+    """tests/bench_sdpa.c compiled unmodified against this library: its six shapes
+    (32 heads x 128; full, rectangular and block-causal prefix) run, and its own
+    cross-check of the flash entry points against qw_gpu_sdpa_rect_bf16 (relL2
+    <= 0.1, bench_sdpa.c:226-237) passes.  Its timing lines go to the test log."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "bench_sdpa_cuda")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/bench_sdpa_cuda not built")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    print(res.stdout)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.count("TFLOPS") >= 11 and "FAIL" not in res.stdout, res.stdout
+
+
 # --------------------------------------------------------------------------
 # prologue
 # --------------------------------------------------------------------------

@@ -126,3 +126,39 @@ def test_rowwise_error_conventions(gpu):
     gpu.submit()
     for t in (x, m, r, f):
         gpu.free(t)
+
+
+def test_modulation_row_index_outside_the_tensor_is_reported(gpu):
+    """row_map comes from device memory, so only the kernel can check it: an
+    entry past the modulation tensor is reported at submit (no out-of-bounds
+    read; block 0 stands in) and the context keeps working."""
+    rng = np.random.default_rng(9)
+    rows, width, slots = 8, 256, 4
+    x = workloads.normal_bf16(rng, (rows, width))
+    mod = workloads.normal_bf16(rng, (2, slots, width), 0.0, 0.5)
+    row_map = np.array([0, 1, 0, 7, 1, 0, 1, 0], np.uint32)   # 7 >= 2 maps
+    lib = gpu.lib
+    xt, mt, rt, ot = gpu.bf16(x), gpu.bf16(mod), gpu.u32(row_map), gpu.new_bf16(rows * width)
+    for call in ("norm", "gate"):
+        gpu.begin()
+        if call == "norm":
+            gpu.check(lib.qw_gpu_layer_norm_mod_bf16(gpu.handle, ot, xt, mt, rt, rows, width, slots,
+                                                     1, 1e-6), "norm")
+        else:
+            gpu.check(lib.h3_gpu_gate_bf16(gpu.handle, ot, xt, xt, mt, rt, rows, width, slots, 2),
+                      "gate")
+        assert lib.h3_gpu_submit(gpu.handle) == 0
+        assert "outside the modulation tensor" in gpu.error(), gpu.error()
+        assert np.isfinite(O.bf16_to_f32(gpu.read_bf16(ot, rows * width))).all()
+    # too small a modulation tensor is refused on the host
+    small = gpu.bf16(mod.ravel()[:slots * width - 8])
+    gpu.begin()
+    assert lib.qw_gpu_layer_norm_mod_bf16(gpu.handle, ot, xt, small, rt, rows, width, slots, 1,
+                                          1e-6) == 0
+    assert "less than one" in gpu.error()
+    gpu.submit()
+    good = np.zeros(rows, np.uint32)
+    check_norm(run_norm(gpu, x, mod, good, rows, width, slots, 1),   # and the context still works
+               O.layer_norm_mod(x, mod, good, rows, width, slots, 1, 1e-6))
+    for t in (xt, mt, rt, ot, small):
+        gpu.free(t)
