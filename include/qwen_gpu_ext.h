@@ -178,10 +178,23 @@ void qw_gpu_host_free(void *pointer);
  * context's stream; complete after the next h3_gpu_submit(). */
 int qw_gpu_tensor_read_async(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host,
                              size_t elements);
+/* Copy lanes: two more streams beside the context's own (lane 0, where every op
+ * runs) that carry only copies, so that a host program can overlap the upload of
+ * the next layer's inputs (lane 1), the compute of this layer (lane 0) and the
+ * read-back of the last layer's output (lane 2).  qw_gpu_fence(from, to) orders
+ * everything enqueued on lane `from` so far before whatever is enqueued on lane
+ * `to` next.  Host buffers must be pinned (qw_gpu_host_alloc) and stay valid until
+ * the next h3_gpu_submit, which waits for every lane.  Not inside a graph capture. */
+int qw_gpu_fence(h3_gpu *gpu, int from_lane, int to_lane);
+int qw_gpu_tensor_write_lane(h3_gpu *gpu, h3_gpu_tensor *tensor, const void *host,
+                             size_t elements, int lane);
+int qw_gpu_tensor_read_lane(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host,
+                            size_t elements, int lane);
 /* Select the attention kernel: "sm100" (default; the 256-row blocks of the last,
  * partly filled wave of CTAs run split in two), "sm100-whole" (same kernel, no
- * block is ever split) or "scalar" (diagnostic fp32 kernel).  Returns 0 on an
- * unknown name. */
+ * block is ever split), "sm100-row" (same kernel; with a score bound the softmax
+ * keeps one thread per query row instead of pairing the warpgroups on each
+ * sub-tile) or "scalar" (diagnostic fp32 kernel).  Returns 0 on an unknown name. */
 int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name);
 /* Launches enqueued by this context's ops since creation (own kernels only). */
 uint64_t qw_gpu_kernel_launches(const h3_gpu *gpu);
@@ -196,43 +209,66 @@ qw_gpu_graph *qw_gpu_graph_end(h3_gpu *gpu);
 int qw_gpu_graph_launch(h3_gpu *gpu, qw_gpu_graph *graph);
 void qw_gpu_graph_free(qw_gpu_graph *graph);
 
-/* ---- multi-GPU: heads sharded across one process per GPU --------------- */
+/* ---- multi-GPU: one process per GPU -------------------------------------
+ * The ranks form batch_groups x head_groups.  A batch group owns some of the
+ * batch items (the reference runs the two classifier-free-guidance branches as two
+ * separate forwards, qwen_pipeline.m:376-381 and :396-401, so a branch's output
+ * is only ever needed by that branch); inside a batch group the attention heads
+ * are sharded, nothing is exchanged before attention, and only the per-layer
+ * [rows, heads*128] output is gathered over NVLink. */
 typedef struct qw_gpu_group qw_gpu_group;
 #define QW_GPU_GROUP_ID_BYTES 128
 /* Rank 0 creates the rendezvous id and hands the bytes to every rank by any
- * host channel; each rank then joins with its own context. */
+ * host channel; each rank then joins with its own context (collective, at most
+ * 8 ranks). */
 int qw_gpu_group_new_id(void *id_bytes, char *error, size_t error_size);
 qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int world,
                                 char *error, size_t error_size);
 void qw_gpu_group_free(qw_gpu_group *group);
 int qw_gpu_group_rank(const qw_gpu_group *group);
 int qw_gpu_group_world(const qw_gpu_group *group);
-/* Gather the per-rank attention outputs [rows, heads_local*128] into the full
- * [rows, world*heads_local*128] tensor on every rank (rank g owns head columns
- * [g*heads_local, (g+1)*heads_local)).  Enqueued on the context's stream. */
+/* Split the ranks: rank = batch_index * head_groups + head_index with head_groups
+ * = world / batch_groups.  Same value on every rank, before the first sharded
+ * attention; the default is 1 (every rank shards the heads of every batch item). */
+int qw_gpu_group_set_batch_groups(qw_gpu_group *group, int batch_groups);
+int qw_gpu_group_batch_index(const qw_gpu_group *group);
+int qw_gpu_group_head_index(const qw_gpu_group *group);
+int qw_gpu_group_head_groups(const qw_gpu_group *group);
+/* NCCL comparison path (one batch group only): gather the per-rank attention
+ * outputs [rows, heads_local*128] into the full [rows, world*heads_local*128]
+ * tensor on every rank (rank g owns head columns [g*heads_local, (g+1)*heads_local)).
+ * Enqueued on the context's stream. */
 int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
                                        const h3_gpu_tensor *local, uint32_t rows,
                                        uint32_t heads_local, uint32_t head_dim);
 
-/* Fused gather.  qw_gpu_group_bind_output (collective) maps every rank's `full`
- * buffer into every process over the NVLink peer path; after that
- * qw_gpu_group_attn_block_causal_bf16 runs this rank's heads and its epilogue
- * stores them into head columns [rank*heads_local, (rank+1)*heads_local) of
- * the full [batch*rows, world*heads_local*128] output on EVERY rank, followed by
- * a cross-rank barrier: no landing zone, no interleave pass.
- * Up to 4 outputs can be bound; alternate between two when a consumer may
- * still read layer L's output while another rank already stores layer L+1.
- * Arguments as qw_gpu_attn_block_causal_bf16 with this rank's head counts. */
+/* Sharded attention with this library's own gather.
+ * qw_gpu_group_bind_output (collective, outside a graph capture) maps every rank's
+ * `full` buffer into every process over the NVLink peer path.  After that
+ * qw_gpu_group_attn_block_causal_bf16 runs this rank's heads_local heads of its
+ * batch group's `batch` items into head columns [head_index*heads_local,
+ * +heads_local) of its own `full` [batch*rows, head_groups*heads_local*128], and a
+ * push kernel on the group's own stream copies that column slice into the same
+ * place of every peer's `full`, under whatever the context's stream runs next.
+ * Ranks hand-shake through epoch flags in peer-mapped memory (a rank stores into a
+ * peer's buffer only after the peer's next attention on that buffer has begun,
+ * i.e. after everything the peer enqueued to read the old contents; every wait is
+ * bounded and reports through h3_gpu_submit).  No landing zone, no interleave pass,
+ * no NCCL call per layer.
+ * Up to 4 outputs can be bound; alternate between two so that layer L's gather
+ * overlaps layer L+1.  score_bound as in qw_gpu_attn_block_causal_bounded_bf16, or
+ * NULL.  The other arguments as qw_gpu_attn_block_causal_bf16 with this rank's
+ * head counts and its batch group's items. */
 int qw_gpu_group_bind_output(qw_gpu_group *group, h3_gpu_tensor *full);
 int qw_gpu_group_barrier(qw_gpu_group *group);
-/* The barrier behind a fused gather runs on the group's own stream so that an
- * independent next layer need not wait for it.  Before enqueueing a consumer of
- * `full`, make the context's stream wait for it; h3_gpu_submit waits anyway. */
+/* Before enqueueing a consumer of `full`, make the context's stream wait until
+ * every peer's columns have landed in it; h3_gpu_submit waits anyway. */
 int qw_gpu_group_wait_output(qw_gpu_group *group, const h3_gpu_tensor *full);
 int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
                                         const h3_gpu_tensor *query, const h3_gpu_tensor *key,
                                         const h3_gpu_tensor *value,
-                                        const h3_gpu_tensor *kv_limit, uint32_t batch,
+                                        const h3_gpu_tensor *kv_limit,
+                                        const h3_gpu_tensor *score_bound, uint32_t batch,
                                         uint32_t rows, uint32_t heads_local,
                                         uint32_t kv_heads_local, uint32_t head_dim,
                                         const uint32_t *text_len, uint32_t text_pad, float scale);

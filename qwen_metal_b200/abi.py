@@ -120,6 +120,9 @@ _SIGNATURES = {
     "qw_gpu_host_alloc": (C.c_void_p, [size_t]),
     "qw_gpu_host_free": (None, [C.c_void_p]),
     "qw_gpu_tensor_read_async": (C.c_int, [c_gpu, c_tensor, C.c_void_p, size_t]),
+    "qw_gpu_fence": (C.c_int, [c_gpu, C.c_int, C.c_int]),
+    "qw_gpu_tensor_write_lane": (C.c_int, [c_gpu, c_tensor, C.c_void_p, size_t, C.c_int]),
+    "qw_gpu_tensor_read_lane": (C.c_int, [c_gpu, c_tensor, C.c_void_p, size_t, C.c_int]),
     "qw_gpu_set_attention_kernel": (C.c_int, [c_gpu, C.c_char_p]),
     "qw_gpu_kernel_launches": (C.c_uint64, [c_gpu]),
     "qw_gpu_graph_begin": (C.c_int, [c_gpu]),
@@ -136,8 +139,12 @@ _SIGNATURES = {
     "qw_gpu_group_barrier": (C.c_int, [C.c_void_p]),
     "qw_gpu_group_wait_output": (C.c_int, [C.c_void_p, c_tensor]),
     "qw_gpu_group_attn_block_causal_bf16": (
-        C.c_int, [C.c_void_p, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32,
-                  u32, C.c_void_p, u32, f32]),
+        C.c_int, [C.c_void_p, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32,
+                  u32, u32, u32, C.c_void_p, u32, f32]),
+    "qw_gpu_group_set_batch_groups": (C.c_int, [C.c_void_p, C.c_int]),
+    "qw_gpu_group_batch_index": (C.c_int, [C.c_void_p]),
+    "qw_gpu_group_head_index": (C.c_int, [C.c_void_p]),
+    "qw_gpu_group_head_groups": (C.c_int, [C.c_void_p]),
     "qw_dit_prefix_limits": (None, [C.POINTER(Segment), u32, C.c_void_p]),
     "qw_pipe_rope_tables": (
         C.c_int, [c_gpu, u32, u32, u32, C.POINTER(c_tensor), C.POINTER(c_tensor), C.c_char_p, size_t]),

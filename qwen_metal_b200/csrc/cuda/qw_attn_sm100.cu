@@ -107,6 +107,8 @@ struct __align__(16) SharedControl {
     int tile_first[2], tile_count[2];
     float merge_m[kTileM];  // split form: sub-tile 1's reference exponent and row sum
     float merge_l[kTileM];
+    // Paired organisation: row sums of the two key halves, [key half][sub-tile][row].
+    float pair_l[2][2][kTileM];
 };
 
 constexpr size_t kSmemData = (size_t)(2 + kStages) * kTileBytes;
@@ -131,6 +133,7 @@ struct KernelParams {
     // score_bound[1], so |q.k| <= their product and the softmax can use one fixed
     // reference exponent instead of a running row maximum.
     const float *score_bound;
+    int pair_org;  // fixed-exponent softmax: both warpgroups share each sub-tile's keys
     int head_major_out;
     // Sharded runs: the same rows are stored into every rank's full output
     // (peer-mapped pointers, plain stores over NVLink).  out_heads_total is the
@@ -140,6 +143,11 @@ struct KernelParams {
     // Launch geometry: CTA c < total_units - tail_units runs unit c whole; the
     // last tail_units units run in split form, two CTAs each.
     uint32_t n_qblocks, total_units, tail_units;
+    // Gather by a separate push: epoch counter of the output slot and the peers'
+    // flag words that receive the new epoch when this kernel starts.
+    uint32_t *slot_use;
+    uint32_t *freed_peer[8];
+    uint32_t n_freed;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -152,6 +160,14 @@ __device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t coun
 
 __device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// The P and staging barriers count one arrival per softmax warp of the CTA (8).
+// Where only one warpgroup works on a sub-tile, each of its four warps arrives
+// for two.
+__device__ __forceinline__ void mbar_arrive_twice(unsigned long long *bar) {
+    mbar_arrive(bar);
+    mbar_arrive(bar);
 }
 
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, uint32_t bytes) {
@@ -498,6 +514,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
                 uint32_t(&cur)[32] = (chunk & 1) ? sb : sa;
                 uint32_t(&nxt)[32] = (chunk & 1) ? sa : sb;
                 QW_TMEM_WAIT_LD32(cur);
+                if (chunk == 0 && tid_in_group == 0) QW_TRACE(sub, 1, j);
                 if (chunk < 3) QW_TMEM_LD32(tmem_s + 32 * (chunk + 1), nxt);
                 if (boundary) {
 #pragma unroll
@@ -526,10 +543,12 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
                 }
                 // P chunk c lands on columns [16c, 16c+16): scores already consumed.
                 QW_TMEM_ST16(tmem_s + chunk * 16, pk);
+                if (chunk == 1 && tid_in_group == 0) QW_TRACE(sub, 2, j);
             }
+            if (tid_in_group == 0) QW_TRACE(sub, 3, j);
             tmem_wait_st();
             tc_fence_before();
-            if ((tid_in_group & 31) == 0) mbar_arrive(bar_p);
+            if ((tid_in_group & 31) == 0) mbar_arrive_twice(bar_p);
             if (tid_in_group == 0) QW_TRACE(sub, 4, j);
             ++processed;
         }
@@ -645,7 +664,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         if (tid_in_group == 0) QW_TRACE(sub, 3, j);
         tmem_wait_st();  // warp-collective: every lane's stores have landed
         tc_fence_before();
-        if ((tid_in_group & 31) == 0) mbar_arrive(bar_p);  // one arrival per warp
+        if ((tid_in_group & 31) == 0) mbar_arrive_twice(bar_p);  // stands for two warps
         if (tid_in_group == 0) QW_TRACE(sub, 4, j);
         sum_a = fadd2(sum_a, sum_b);
         l_run += sum_a.x + sum_a.y;
@@ -762,7 +781,7 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
     if (p.head_major_out) return;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> TMA reads
     __syncwarp();
-    if ((tid_in_group & 31) == 0) mbar_arrive(&ctl->bars[kBarEpi + sub]);
+    if ((tid_in_group & 31) == 0) mbar_arrive_twice(&ctl->bars[kBarEpi + sub]);
     if (tid_in_group == 0) {
         if (!mbar_wait(ctl, &ctl->bars[kBarEpi + sub], 0, p.status,
                        (1u << 16) | (uint32_t)(kBarEpi + sub), 0xfffcu))
@@ -778,6 +797,223 @@ __device__ __forceinline__ void softmax_role(const KernelParams &p, SharedContro
         // what the barrier behind a sharded launch waits for.
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
+}
+
+// ---------------------------------------------------------------------------
+// Paired softmax role (fixed reference exponent only): all 256 softmax threads
+// work on one sub-tile's scores at a time, then on the other's.  TMEM lanes are
+// tied to warp_id % 4, so warps w and w + 4 both reach rows 32w..32w+31 of either
+// sub-tile: thread (half, r) takes keys [64*half, 64*half + 64) of row r.  Two
+// warps per scheduler run the exponentials of one tile together, which halves
+// the time a tile's S -> P step stays on the dependency chain S -> P -> P V; the
+// other sub-tile's MMAs fill the tensor pipe meanwhile.  Without a row maximum
+// the two threads of a row share nothing until the row sums meet at the end.
+// ---------------------------------------------------------------------------
+template <int kPoly>
+__device__ __forceinline__ void softmax_pair_role(const KernelParams &p, SharedControl *ctl,
+                                                  const OutMaps &maps_out, uint8_t *smem_q,
+                                                  int tid, int limit0, int limit1, uint32_t b,
+                                                  uint32_t h, uint32_t row0, bool split,
+                                                  float bound) {
+    const int half = tid >> 7, r = tid & 127;
+    const uint32_t lane_base = (uint32_t)((r >> 5) * 32) << 16;
+    const uint32_t tmem = ctl->tmem_base + lane_base;
+    const uint32_t s_col[2] = {kTmemS0 + 64u * (uint32_t)half, kTmemS1 + 64u * (uint32_t)half};
+    const int limits[2] = {limit0, limit1};
+    const int pad_lo = p.text_pad ? (int)p.text_len[b] : 0;
+    const int pad_hi = (int)p.text_pad;
+    const float2 cs2 = make_float2(p.scale_log2, p.scale_log2);
+    const float2 bias2 = make_float2(-bound, -bound);
+    [[maybe_unused]] uint32_t trace_cursor = 0;
+
+    float2 sums[2][2] = {{make_float2(0.f, 0.f), make_float2(0.f, 0.f)},
+                         {make_float2(0.f, 0.f), make_float2(0.f, 0.f)}};
+    uint32_t phase[2] = {0, 0};
+    const int first[2] = {ctl->tile_first[0], ctl->tile_first[1]};
+    const int count[2] = {ctl->tile_count[0], ctl->tile_count[1]};
+    const int steps = max(count[0], count[1]);
+    bool ok = true;
+    // The first 32 scores of the next tile (the other sub-tile's, as a rule complete
+    // long before) are requested while this tile's last P chunk is still on its way
+    // to TMEM, so a tile does not start with an exposed TMEM round trip.
+    bool prefetched = false;
+    uint32_t sa[32], sb[32];
+
+    for (int s = 0; s < steps && ok; ++s) {
+#pragma unroll
+        for (int sub = 0; sub < 2; ++sub) {
+            if (s >= count[sub] || !ok) continue;
+            const int j = phys_tile(ctl, first[sub] + s);
+            if (!prefetched) {
+                ok = mbar_wait(ctl, &ctl->bars[kBarSFull + sub], phase[sub], p.status,
+                               (1u << 16) | (uint32_t)(kBarSFull + sub), (uint32_t)j);
+                if (!ok) continue;
+                phase[sub] ^= 1u;
+                tc_fence_after();
+                QW_TMEM_LD32(tmem + s_col[sub], sa);
+            }
+            prefetched = false;
+            if (tid == 0) QW_TRACE(sub, 0, j);
+            const int key0 = j * kTileN + 64 * half;
+            const int my_limit = limits[sub];
+            const bool pad_hit = pad_hi > pad_lo && key0 < pad_hi && key0 + 64 > pad_lo;
+            const bool boundary = __any_sync(0xffffffffu, key0 + 64 > my_limit) || pad_hit;
+#pragma unroll
+            for (int chunk = 0; chunk < 2; ++chunk) {
+                uint32_t(&cur)[32] = chunk ? sb : sa;
+                QW_TMEM_WAIT_LD32(cur);
+                if (chunk == 0) QW_TMEM_LD32(tmem + s_col[sub] + 32, sb);
+                if (chunk == 0 && tid == 0) QW_TRACE(sub, 1, j);
+                if (boundary) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + chunk * 32 + i;
+                        const bool visible = key < my_limit && !(key >= pad_lo && key < pad_hi);
+                        cur[i] = visible ? cur[i] : __float_as_uint(-INFINITY);
+                    }
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float2 x = ffma2(make_float2(__uint_as_float(cur[2 * i]),
+                                                 __uint_as_float(cur[2 * i + 1])),
+                                     cs2, bias2);
+                    float2 pr;
+                    if ((i & 3) < kPoly) {
+                        pr = exp2_poly2(x);
+                    } else {
+                        pr.x = fast_exp2(x.x);
+                        pr.y = fast_exp2(x.y);
+                    }
+                    sums[sub][i & 1] = fadd2(sums[sub][i & 1], pr);
+                    pk[i] = pack_bf16(pr.x, pr.y);
+                }
+                // P of this thread's keys lands over this thread's own scores.
+                QW_TMEM_ST16(tmem + s_col[sub] + chunk * 16, pk);
+                if (chunk == 0 && tid == 0) QW_TRACE(sub, 2, j);
+            }
+            if (tid == 0) QW_TRACE(sub, 3, j);
+            {
+                const int nsub = 1 - sub, ns = sub ? s + 1 : s;
+                if (ns < count[nsub]) {
+                    const bool ready = mbar_try(&ctl->bars[kBarSFull + nsub], phase[nsub]);
+                    if (__all_sync(0xffffffffu, ready)) {
+                        phase[nsub] ^= 1u;
+                        tc_fence_after();
+                        QW_TMEM_LD32(tmem + s_col[nsub], sa);
+                        prefetched = true;
+                    }
+                }
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            if ((tid & 31) == 0) mbar_arrive(&ctl->bars[kBarPFull + sub]);
+            if (tid == 0) QW_TRACE(sub, 4, j);
+        }
+    }
+    // Row sums of the two key halves meet here.  Every softmax thread reaches this
+    // barrier, also after a wait gave up (its rows are then simply not stored).
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+        const float2 t = fadd2(sums[sub][0], sums[sub][1]);
+        ctl->pair_l[half][sub][r] = t.x + t.y;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    if (!ok || ctl->abort_flag) return;
+
+    // Epilogue.  Whole form: output tile t is sub-tile t, O_t / l_t.  Split form: one
+    // tile whose keys were divided between the sub-tiles: (O_0 + O_1) / (l_0 + l_1);
+    // both carry the same reference exponent, so the sum needs no reweighting.
+    // Thread (half, r) converts columns [64*half, 64*half + 64) of row r: exactly one
+    // 128-byte line of the swizzled staging box of its half.
+    const int n_out_tiles = split ? 1 : 2;
+#pragma unroll 1
+    for (int t = 0; t < n_out_tiles; ++t) {
+        const uint32_t tile_row0 = row0 + (uint32_t)t * kTileM;
+        if (tile_row0 >= p.q_rows) continue;
+        const uint32_t row = tile_row0 + (uint32_t)r;
+        const bool has_row = row < p.q_rows;
+        const bool use0 = split ? count[0] > 0 : count[t] > 0;
+        const bool use1 = split && count[1] > 0;
+        float l = ctl->pair_l[0][t][r] + ctl->pair_l[1][t][r];
+        if (split) l += ctl->pair_l[0][1][r] + ctl->pair_l[1][1][r];
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        if (use0 &&
+            !mbar_wait(ctl, &ctl->bars[kBarOFinal + t], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarOFinal + t), 0xffffu))
+            return;
+        if (use1 &&
+            !mbar_wait(ctl, &ctl->bars[kBarOFinal + 1], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarOFinal + 1), 0xfffeu))
+            return;
+        if (!use0 && !p.head_major_out &&
+            // nothing was computed (zeros go out), but the Q load may still be in
+            // flight into what is now the staging area: let it land first
+            !mbar_wait(ctl, &ctl->bars[kBarQFull + t], 0, p.status,
+                       (1u << 16) | (uint32_t)(kBarQFull + t), 0xfffdu))
+            return;
+        tc_fence_after();
+        const uint32_t o_own = tmem + (t ? kTmemO1 : kTmemO0) + 64u * (uint32_t)half;
+        const uint32_t o_other = tmem + kTmemO1 + 64u * (uint32_t)half;
+        uint8_t *line = smem_q + (size_t)t * kTileBytes + (size_t)half * kHalfTileBytes +
+                        (size_t)r * 128;
+        const int sw = r & 7;
+        __nv_bfloat16 *direct =
+            p.out + (((size_t)b * p.heads + h) * p.q_rows + (has_row ? row : 0u)) * kHeadDim +
+            64 * half;
+#pragma unroll 1
+        for (int chunk = 0; chunk < 2; ++chunk) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+            if (use0) {
+                uint32_t o[32];
+                QW_TMEM_LD32(o_own + chunk * 32, o);
+                QW_TMEM_WAIT_LD32(o);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(o[i]);
+            }
+            if (use1) {
+                uint32_t o[32];
+                QW_TMEM_LD32(o_other + chunk * 32, o);
+                QW_TMEM_WAIT_LD32(o);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(o[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint4 packed;
+                packed.x = pack_bf16(v[i] * inv, v[i + 1] * inv);
+                packed.y = pack_bf16(v[i + 2] * inv, v[i + 3] * inv);
+                packed.z = pack_bf16(v[i + 4] * inv, v[i + 5] * inv);
+                packed.w = pack_bf16(v[i + 6] * inv, v[i + 7] * inv);
+                if (p.head_major_out) {
+                    if (has_row) reinterpret_cast<uint4 *>(direct + chunk * 32)[i >> 3] = packed;
+                } else {
+                    const int c16 = chunk * 4 + (i >> 3);  // 16-byte piece of the 128-byte line
+                    *reinterpret_cast<uint4 *>(line + ((c16 ^ sw) << 4)) = packed;
+                }
+            }
+        }
+        if (p.head_major_out) continue;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> TMA reads
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(&ctl->bars[kBarEpi + t]);
+        if (tid == 0) {
+            if (!mbar_wait(ctl, &ctl->bars[kBarEpi + t], 0, p.status,
+                           (1u << 16) | (uint32_t)(kBarEpi + t), 0xfffcu))
+                return;
+            const uint8_t *stage = smem_q + (size_t)t * kTileBytes;
+            const int col = (int)((p.out_head_offset + h) * kHeadDim);
+            for (uint32_t d = 0; d < p.n_out; ++d) {
+                tma_store_3d(&maps_out.m[d], stage, col, (int)tile_row0, (int)b);
+                tma_store_3d(&maps_out.m[d], stage + kHalfTileBytes, col + 64, (int)tile_row0, (int)b);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+    // Shared memory may be released once the stores have read it.
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -803,19 +1039,23 @@ __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_
 }
 
 __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo,
-                                         bool accumulate) {
+                                         bool accumulate, bool paired) {
     // A = P from TMEM (16 keys = 8 packed columns per step).  B = V, MN-major:
     // 16 keys = 2 groups of 8 rows (1024 B apart), the two 64-wide column
-    // halves one half tile apart.
+    // halves one half tile apart.  P of keys 0..127 sits on columns 0..63 of the
+    // score region; in the paired organisation each key half is written by its own
+    // warp over its own scores, so keys 64..127 sit on columns 64..95.
+    const uint32_t upper = paired ? 64u - 32u : 0u;
 #pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
-        mma_ts(d_tmem, p_tmem + (uint32_t)kk * 8u, v_lo + (uint32_t)(kk * 2048 >> 4), kDescHi,
-               kIdescPV, (accumulate || kk > 0) ? 1u : 0u);
+        const uint32_t col = (uint32_t)kk * 8u + (kk >= 4 ? upper : 0u);
+        mma_ts(d_tmem, p_tmem + col, v_lo + (uint32_t)(kk * 2048 >> 4), kDescHi, kIdescPV,
+               (accumulate || kk > 0) ? 1u : 0u);
     }
 }
 
 __device__ __forceinline__ void mma_role(const KernelParams &p, SharedControl *ctl,
-                                         uint8_t *smem_q, uint8_t *smem_kv) {
+                                         uint8_t *smem_q, uint8_t *smem_kv, bool paired) {
     // Whole form: both sub-tiles walk the visited tiles from 0; u counts them.
     const int n0 = ctl->tile_count[0], n1 = ctl->tile_count[1];
     const int n_max = max(n0, n1);
@@ -884,7 +1124,7 @@ __device__ __forceinline__ void mma_role(const KernelParams &p, SharedControl *c
                 p_phase[i] ^= 1u;
                 tc_fence_after();
                 QW_TRACE(2, i, j);
-                issue_pv(o_tmem[i], s_tmem[i], v_lo, o_started[i]);
+                issue_pv(o_tmem[i], s_tmem[i], v_lo, o_started[i], paired);
                 o_started[i] = true;
                 QW_TRACE(2, 4 + i, j);
             }
@@ -933,7 +1173,7 @@ __device__ __forceinline__ uint32_t pair_a(int s, int lb) { return 2u * (uint32_
 __device__ __forceinline__ uint32_t pair_b(int s) { return 2u * (uint32_t)(2 * s + 1); }
 
 __device__ __forceinline__ void mma_role_split(const KernelParams &p, SharedControl *ctl,
-                                               uint8_t *smem_q, uint8_t *smem_kv) {
+                                               uint8_t *smem_q, uint8_t *smem_kv, bool paired) {
     const int la = ctl->tile_count[0], lb = ctl->tile_count[1];
     if (la <= 0) return;
     const uint32_t tmem = ctl->tmem_base;
@@ -980,7 +1220,7 @@ __device__ __forceinline__ void mma_role_split(const KernelParams &p, SharedCont
                 return;
             p_phase[i] ^= 1u;
             tc_fence_after();
-            issue_pv(o_tmem[i], s_tmem[i], desc, s > 0);
+            issue_pv(o_tmem[i], s_tmem[i], desc, s > 0, paired);
             QW_RING_FREE(t_now + 1);
             if (s + 1 < count) {
                 const uint32_t t_next = i ? pair_b(s + 1) : pair_a(s + 1, lb);
@@ -1101,9 +1341,9 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctl->bars[kBarSFull + i], 1);
-            mbar_init(&ctl->bars[kBarPFull + i], kTileM / 32);
+            mbar_init(&ctl->bars[kBarPFull + i], kSoftmaxThreads / 32);
             mbar_init(&ctl->bars[kBarOFinal + i], 1);
-            mbar_init(&ctl->bars[kBarEpi + i], kTileM / 32);
+            mbar_init(&ctl->bars[kBarEpi + i], kSoftmaxThreads / 32);
         }
         mbar_init(&ctl->bars[kBarMerge], kTileM / 32);
         mbar_init(&ctl->bars[kBarDebug], 1);
@@ -1131,6 +1371,16 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
             tma_load_3d(dst + kHalfTileBytes, map, bar, col + 64, j0 * kTileN, (int)b);
         }
     }
+    if (blockIdx.x == 0 && warp == 10 && lane == 0 && p.slot_use) {
+        // Sharded heads: whatever read this output slot's previous contents was
+        // enqueued before this kernel, so the peers may store the new epoch now.
+        const uint32_t epoch = *p.slot_use + 1u;
+        *p.slot_use = epoch;
+        __threadfence_system();
+        for (uint32_t d = 0; d < p.n_freed; ++d)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.freed_peer[d]), "r"(epoch)
+                         : "memory");
+    }
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&ctl->tmem_base)),
@@ -1149,16 +1399,25 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     // the running-maximum softmax: no promise given, or one too loose to keep
     // exp2(score*c - bound) >= 2^-2*bound inside the normal fp32 range.
     float bound = -1.0f;
+    if (kMayBound && p.score_bound) {  // every role needs to know which softmax runs
+        const float limit = ceilf(p.score_bound[0] * p.score_bound[1] * p.scale_log2);
+        if (limit >= 0.0f && limit <= 60.0f) bound = limit;
+    }
+    // Paired organisation of the fixed-exponent softmax (both warpgroups on one
+    // sub-tile at a time) unless the launch asks for one thread per row.
+    const bool paired = kMayBound && bound >= 0.0f && p.pair_org;
+    int other_limit = 0;
     if (tid < kSoftmaxThreads) {
-        if (kMayBound && p.score_bound) {
-            const float limit = ceilf(p.score_bound[0] * p.score_bound[1] * p.scale_log2);
-            if (limit >= 0.0f && limit <= 60.0f) bound = limit;
-        }
         sub = tid >> 7;
         tid_in_group = tid & 127;
         // (split form: both warpgroups work on the same 128 rows)
         my_row = row0 + (split ? 0u : (uint32_t)sub * kTileM) + (uint32_t)tid_in_group;
         my_limit = row_limit(p, b, my_row);
+        // (paired: this thread also works on the same row of the other sub-tile)
+        if (paired)
+            other_limit = split ? my_limit
+                                : row_limit(p, b, row0 + (uint32_t)(1 - sub) * kTileM +
+                                                      (uint32_t)tid_in_group);
         int warp_max = my_limit;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1)
@@ -1190,7 +1449,10 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
         uint8_t *stage = smem_q + (size_t)sub * kTileBytes;
         const uint32_t tile_row0 = split ? row0 : row0 + (uint32_t)sub * kTileM;
-        if (kMayBound && bound >= 0.0f)
+        if (paired)
+            softmax_pair_role<kPoly>(p, ctl, maps_out, smem_q, tid, sub ? other_limit : my_limit,
+                                     sub ? my_limit : other_limit, b, h, row0, split, bound);
+        else if (kMayBound && bound >= 0.0f)
             softmax_role<kPoly, kMayBound>(p, ctl, maps_out, stage, sub, tid_in_group, my_limit, b,
                                            h, my_row, tile_row0, split, bound);
         else
@@ -1202,8 +1464,8 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
     if (tid < kSoftmaxThreads) {
     } else if (warp == kMmaWarp) {
         if (lane == 0) {
-            if (split) mma_role_split(p, ctl, smem_q, smem_kv);
-            else mma_role(p, ctl, smem_q, smem_kv);
+            if (split) mma_role_split(p, ctl, smem_q, smem_kv, paired);
+            else mma_role(p, ctl, smem_q, smem_kv, paired);
         }
     } else if (warp == kTmaWarp && lane == 0) {
         tma_role(p, ctl, smem_kv, &map_k, &map_v, b, kvh, split);
@@ -1322,6 +1584,17 @@ bool whole_units_forced() {
     return forced != 0;
 }
 
+// QW_CUDA_SOFTMAX_ORG=row: run the fixed-exponent softmax with one thread per row
+// (one warpgroup per sub-tile) instead of the paired organisation (comparison runs).
+bool row_org_forced() {
+    static int forced = -1;
+    if (forced < 0) {
+        const char *env = getenv("QW_CUDA_SOFTMAX_ORG");
+        forced = env && !strcmp(env, "row") ? 1 : 0;
+    }
+    return forced != 0;
+}
+
 // The kernel variants: how many of every 4 score pairs take the polynomial exp2
 // (QW_CUDA_EXP_POLY=0..2 overrides the default for tuning), with or without the
 // fixed-exponent softmax for callers that pass a score bound.  The opt-in to
@@ -1397,6 +1670,7 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     p.text_pad = a->text_pad;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.score_bound = a->score_bound;
+    p.pair_org = (a->row_softmax || row_org_forced()) ? 0 : 1;
     p.head_major_out = a->head_major_out;
     if (a->n_out_peers > 0) {
         if (a->n_out_peers > 8 || a->head_major_out) return (int)cudaErrorInvalidValue;
@@ -1413,6 +1687,10 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
         p.out_heads_total = a->heads;
         p.out_head_offset = 0;
     }
+    p.slot_use = a->slot_use;
+    p.n_freed = a->slot_use ? a->n_freed : 0;
+    if (p.n_freed > 8) return (int)cudaErrorInvalidValue;
+    for (uint32_t d = 0; d < 8; ++d) p.freed_peer[d] = d < p.n_freed ? a->freed_peer[d] : nullptr;
     OutMaps maps_out;
     memset(&maps_out, 0, sizeof(maps_out));
     if (!p.head_major_out)

@@ -211,6 +211,9 @@ void h3_gpu_free(h3_gpu *gpu) {
     if (gpu->chain_start) cudaEventDestroy(gpu->chain_start);
     if (gpu->chain_stop) cudaEventDestroy(gpu->chain_stop);
     if (gpu->aux_joined) cudaEventDestroy(gpu->aux_joined);
+    if (gpu->lane_event) cudaEventDestroy(gpu->lane_event);
+    for (int lane = 1; lane < 3; lane++)
+        if (gpu->lane[lane]) cudaStreamDestroy(gpu->lane[lane]);
     if (gpu->stream) cudaStreamDestroy(gpu->stream);
     cudaGetLastError();
     free(gpu);
@@ -224,6 +227,7 @@ int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name) {
     if (!gpu || !name) return 0;
     if (!strcmp(name, "sm100")) gpu->attn_kernel = QW_ATTN_SM100;
     else if (!strcmp(name, "sm100-whole")) gpu->attn_kernel = QW_ATTN_SM100_WHOLE;
+    else if (!strcmp(name, "sm100-row")) gpu->attn_kernel = QW_ATTN_SM100_ROW;
     else if (!strcmp(name, "scalar")) gpu->attn_kernel = QW_ATTN_SCALAR;
     else {
         qw_set_error(gpu, "unknown attention kernel '%s'", name);
@@ -393,6 +397,81 @@ int qw_gpu_tensor_read_async(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *hos
                       "asynchronous tensor read");
 }
 
+/* ---- copy lanes (no counterpart in the reference) -------------------------
+ * A host program that streams inputs in and results out overlaps three things:
+ * the upload of the next layer, the compute of this one, the read-back of the
+ * last.  Lane 0 is the context's stream (every op runs there); lanes 1 and 2 are
+ * two more streams that only carry copies.  qw_gpu_fence(from, to) orders
+ * everything enqueued on `from` so far before whatever is enqueued on `to` next.
+ * Host buffers must be pinned (qw_gpu_host_alloc) and stay valid until the next
+ * h3_gpu_submit, which waits for all lanes. */
+#define QW_LANES 3
+static cudaStream_t lane_stream(h3_gpu *gpu, int lane) {
+    if (lane < 0 || lane >= QW_LANES) return NULL;
+    if (lane == 0) return gpu->stream;
+    if (!gpu->lane[lane] &&
+        cudaStreamCreateWithFlags(&gpu->lane[lane], cudaStreamNonBlocking) != cudaSuccess) {
+        cudaGetLastError();
+        gpu->lane[lane] = NULL;
+    }
+    return gpu->lane[lane];
+}
+
+int qw_gpu_fence(h3_gpu *gpu, int from_lane, int to_lane) {
+    if (!gpu || !qw_bind(gpu)) return 0;
+    if (gpu->capturing) {
+        qw_set_error(gpu, "copy lanes cannot be used inside a graph capture");
+        return 0;
+    }
+    cudaStream_t from = lane_stream(gpu, from_lane), to = lane_stream(gpu, to_lane);
+    if (!from || !to) {
+        qw_set_error(gpu, "fence: no such lane (0..%d)", QW_LANES - 1);
+        return 0;
+    }
+    if (from == to) return 1;
+    /* One event per fence call would leak; a single event re-recorded is fine:
+     * cudaStreamWaitEvent captures the record that is current when it is called. */
+    if (!gpu->lane_event &&
+        !qw_cuda_ok(gpu, cudaEventCreateWithFlags(&gpu->lane_event, cudaEventDisableTiming),
+                    "fence event"))
+        return 0;
+    return qw_cuda_ok(gpu, cudaEventRecord(gpu->lane_event, from), "fence record") &&
+           qw_cuda_ok(gpu, cudaStreamWaitEvent(to, gpu->lane_event, 0), "fence wait");
+}
+
+static int lane_copy(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host, size_t elements,
+                     int lane, int to_device) {
+    if (!gpu || !tensor || !host || tensor->owner != gpu || elements > tensor->elements ||
+        !qw_bind(gpu))
+        return 0;
+    if (gpu->capturing) {
+        qw_set_error(gpu, "copy lanes cannot be used inside a graph capture");
+        return 0;
+    }
+    cudaStream_t stream = lane_stream(gpu, lane);
+    if (!stream) {
+        qw_set_error(gpu, "lane copy: no such lane (0..%d)", QW_LANES - 1);
+        return 0;
+    }
+    size_t bytes = elements * qw_dtype_size(tensor->dtype);
+    return qw_cuda_ok(gpu,
+                      to_device ? cudaMemcpyAsync(tensor->dev, host, bytes, cudaMemcpyHostToDevice,
+                                                  stream)
+                                : cudaMemcpyAsync(host, tensor->dev, bytes, cudaMemcpyDeviceToHost,
+                                                  stream),
+                      to_device ? "lane upload" : "lane read-back");
+}
+
+int qw_gpu_tensor_write_lane(h3_gpu *gpu, h3_gpu_tensor *tensor, const void *host,
+                             size_t elements, int lane) {
+    return lane_copy(gpu, tensor, (void *)host, elements, lane, 1);
+}
+
+int qw_gpu_tensor_read_lane(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host,
+                            size_t elements, int lane) {
+    return lane_copy(gpu, tensor, host, elements, lane, 0);
+}
+
 void *qw_gpu_host_alloc(size_t bytes) {
     void *pointer = NULL;
     if (!bytes || cudaMallocHost(&pointer, bytes) != cudaSuccess) {
@@ -439,6 +518,8 @@ int h3_gpu_submit(h3_gpu *gpu) {
         if (gpu->aux_joined && cudaEventRecord(gpu->aux_joined, gpu->aux_stream) == cudaSuccess)
             cudaStreamWaitEvent(gpu->stream, gpu->aux_joined, 0);
     }
+    for (int lane = 1; lane < QW_LANES; lane++) /* copies on the other lanes belong to the chain */
+        if (gpu->lane[lane]) qw_gpu_fence(gpu, lane, 0);
     cudaEventRecord(gpu->chain_stop, gpu->stream);
     cudaMemcpyAsync(gpu->status_host, gpu->status_dev, QWCU_STATUS_WORDS * sizeof(uint32_t),
                     cudaMemcpyDeviceToHost, gpu->stream);

@@ -72,9 +72,19 @@ typedef struct {
     uint32_t out_heads_total;
     uint32_t out_head_offset;
     uint32_t *status; /* QWCU_STATUS_WORDS device words, zero when healthy */
+    /* Sharded heads with the gather as a separate push (cuda/qw_push.cu): at its
+     * start the kernel increments *slot_use and stores the new epoch into
+     * freed_peer[0..n_freed) (peer-mapped flag words): the peers may now store
+     * their columns of this epoch into this rank's output slot. */
+    uint32_t *slot_use;
+    uint32_t *freed_peer[8];
+    uint32_t n_freed;
     /* sm100 kernel: never run the units of the last wave in split form (two CTAs
      * per 256-row block, key tiles divided between the sub-tiles). */
     int whole_units;
+    /* sm100 kernel with a score bound: one thread per query row (one warpgroup per
+     * sub-tile) instead of both warpgroups sharing each sub-tile's keys. */
+    int row_softmax;
 } qwcu_attn_args;
 
 /* tcgen05/TMEM/TMA flash-attention forward (sm_100a). */
@@ -143,6 +153,32 @@ int qwcu_gate_launch(const qwcu_rowwise_args *args, int sm_count, qwcu_stream st
 /* h3 causal variant helper: out = bf16(in * scale), elementwise. */
 int qwcu_scale_bf16_launch(void *out, const void *in, size_t elements, float scale,
                            qwcu_stream stream);
+
+/* Sharded heads: copy this rank's column slice of its full output into the same
+ * place of every peer's output (peer-mapped pointers) and hand-shake with the
+ * peers through epoch flags; see cuda/qw_push.cu.  All flag pointers are device
+ * addresses: *_local in this rank's memory, ready_peer[d] in peer d's. */
+typedef struct {
+    const void *src;       /* this rank's full output [rows][row_bytes] */
+    void *dst[8];          /* the peers' full outputs */
+    uint32_t peer_rank[8]; /* the peers' indices into the 8-entry flag rows */
+    uint32_t n_peers;
+    uint32_t my_rank;
+    uint32_t rows;
+    uint32_t row_bytes;   /* bytes per output row */
+    uint32_t col_byte0;   /* first byte of this rank's column slice in a row */
+    uint32_t slice_bytes; /* bytes of the slice */
+    const uint32_t *slot_use;    /* epoch counter of the output slot */
+    const uint32_t *freed_local; /* [8] peers' "your stores may start" flags */
+    const uint32_t *ready_local; /* [8] peers' "my columns have landed" flags */
+    uint32_t *ready_peer[8];     /* where this rank reports to peer d */
+    uint32_t *arrivals;          /* zero-initialised CTA counter of the slot */
+    uint32_t *status;
+    uint32_t wait_ms;    /* budget of every flag wait (0 = 2000 ms) */
+    uint32_t max_blocks; /* CTAs of 256 threads (0 = 32) */
+} qwcu_push_args;
+
+int qwcu_push_launch(const qwcu_push_args *args, qwcu_stream stream);
 
 /* Multi-GPU gather epilogue: staged [world][rows][slice] -> full [rows][world*slice]
  * (bf16 elements; slice_elements must be a multiple of 8). */

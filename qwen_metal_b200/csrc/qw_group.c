@@ -1,5 +1,9 @@
-/* Multi-GPU group: one process per GPU, attention heads sharded across ranks,
- * the per-layer [rows, heads*128] output gathered over NVLink with NCCL.
+/* Multi-GPU group: one process per GPU.  The ranks form batch_groups x
+ * head_groups: a batch group owns some of the batch items (the two branches of
+ * classifier-free guidance, which the reference runs as two separate forwards:
+ * qwen_pipeline.m:376-381, :396-401), inside it the attention heads are sharded
+ * and only the per-layer [rows, heads*128] output is gathered over NVLink, by
+ * this library's own push kernel (cuda/qw_push.cu) or, for comparison, by NCCL.
  *
  * NCCL is bound at run time (dlopen of libnccl.so.2) so the library loads on a
  * machine without it and shares the copy a host program already loaded.  The
@@ -66,29 +70,92 @@ static int nccl_bind(char *error, size_t error_size) {
 #define QW_IPC_HANDLE_BYTES 64
 #define QW_GROUP_MAX_BOUND 4
 
+/* Flag block of a rank (uint32 words, peer-mapped on every rank):
+ *   [0, 4)    slot_use[slot]   epoch counter, incremented by the attention kernel
+ *   [4, 8)    arrivals[slot]   CTA counter of the push kernel
+ *   [8, 40)   freed[slot][r]   written by rank r: its slot may be stored into
+ *   [40, 72)  ready[slot][r]   written by rank r: its columns have landed here */
+#define QW_SYNC_WORDS 128
+#define QW_SYNC_USE(slot) (slot)
+#define QW_SYNC_ARRIVALS(slot) (4 + (slot))
+#define QW_SYNC_FREED(slot, r) (8 + (slot) * QW_GROUP_MAX_WORLD + (r))
+#define QW_SYNC_READY(slot, r) (40 + (slot) * QW_GROUP_MAX_WORLD + (r))
+
 struct qw_gpu_group {
     h3_gpu *gpu;
     nccl_comm_t comm;
     int rank, world;
-    void *staging; /* [world][rows][slice] landing zone of the collective */
+    /* rank = batch_index * head_groups + head_index; peers = the other ranks of
+     * this rank's batch group, the only ones it exchanges output columns with. */
+    int batch_groups, head_groups, batch_index, head_index;
+    int peers[QW_GROUP_MAX_WORLD], n_peers;
+    void *staging; /* [world][rows][slice] landing zone of the NCCL collective */
     size_t staging_bytes;
     int sm_count;
-    /* Fused gather: every rank's full output buffer mapped into this process. */
     unsigned char *exchange; /* device: world * 64-byte IPC handles, then one float */
-    /* Up to QW_GROUP_MAX_BOUND outputs can be bound at once (a consumer that is
-     * still reading layer L's output on one rank must not see another rank's
-     * layer L+1 stores: alternate between two bound buffers). */
+    uint32_t *sync_peer[QW_GROUP_MAX_WORLD]; /* every rank's flag block ([rank] = own) */
+    /* Up to QW_GROUP_MAX_BOUND outputs can be bound at once; a layer's gather runs
+     * under the next layer's compute, so consecutive layers alternate between two. */
     h3_gpu_tensor *bound[QW_GROUP_MAX_BOUND];
     void *peer_out[QW_GROUP_MAX_BOUND][QW_GROUP_MAX_WORLD];
-    /* The barrier that completes a fused gather runs on its own stream so the
-     * next (independent) layer does not wait for it; slot_done[b] marks the
-     * last barrier that covered bound output b. */
+    /* The push runs on its own stream; slot_done[b] marks the end of the last one
+     * that covered bound output b (all ranks' columns present). */
     cudaStream_t comm_stream;
     cudaEvent_t kernel_done;
     cudaEvent_t slot_done[QW_GROUP_MAX_BOUND];
     int slot_pending[QW_GROUP_MAX_BOUND];
     uint32_t slot_capture[QW_GROUP_MAX_BOUND]; /* capture the slot's event belongs to (0 = none) */
+    uint32_t push_blocks, wait_ms;
 };
+
+static void group_layout(qw_gpu_group *group, int batch_groups) {
+    group->batch_groups = batch_groups;
+    group->head_groups = group->world / batch_groups;
+    group->batch_index = group->rank / group->head_groups;
+    group->head_index = group->rank % group->head_groups;
+    group->n_peers = 0;
+    for (int k = 0; k < group->head_groups; k++)
+        if (k != group->head_index)
+            group->peers[group->n_peers++] = group->batch_index * group->head_groups + k;
+}
+
+/* Collective: every rank contributes the device allocation `mine`; on return
+ * peers[r] is rank r's allocation mapped into this process (CUDA IPC over the
+ * NVLink peer path), peers[rank] = mine.  The handles travel through the group's
+ * NCCL communicator. */
+static int exchange_and_open(qw_gpu_group *group, void *mine, void **peers, const char *what) {
+    h3_gpu *gpu = group->gpu;
+    cudaIpcMemHandle_t handle;
+    if (!qw_cuda_ok(gpu, cudaIpcGetMemHandle(&handle, mine), "cudaIpcGetMemHandle")) return 0;
+    unsigned char host[QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES];
+    unsigned char *slot = group->exchange + (size_t)group->rank * QW_IPC_HANDLE_BYTES;
+    if (!qw_cuda_ok(gpu, cudaMemcpyAsync(slot, &handle, QW_IPC_HANDLE_BYTES, cudaMemcpyHostToDevice,
+                                         gpu->stream), "handle upload"))
+        return 0;
+    int rc = g_nccl.all_gather(slot, group->exchange, QW_IPC_HANDLE_BYTES, NCCL_UINT8, group->comm,
+                               gpu->stream);
+    if (rc) {
+        qw_set_error(gpu, "ncclAllGather (%s handles): %s", what, g_nccl.get_error_string(rc));
+        return 0;
+    }
+    if (!qw_cuda_ok(gpu, cudaMemcpyAsync(host, group->exchange,
+                                         (size_t)group->world * QW_IPC_HANDLE_BYTES,
+                                         cudaMemcpyDeviceToHost, gpu->stream), "handle download") ||
+        !qw_cuda_ok(gpu, cudaStreamSynchronize(gpu->stream), "handle exchange"))
+        return 0;
+    for (int r = 0; r < group->world; r++) {
+        if (r == group->rank) {
+            peers[r] = mine;
+            continue;
+        }
+        cudaIpcMemHandle_t theirs;
+        memcpy(&theirs, host + (size_t)r * QW_IPC_HANDLE_BYTES, QW_IPC_HANDLE_BYTES);
+        if (!qw_cuda_ok(gpu, cudaIpcOpenMemHandle(&peers[r], theirs, cudaIpcMemLazyEnablePeerAccess),
+                        "cudaIpcOpenMemHandle"))
+            return 0;
+    }
+    return 1;
+}
 
 int qw_gpu_group_new_id(void *id_bytes, char *error, size_t error_size) {
     if (!id_bytes || !nccl_bind(error, error_size)) return 0;
@@ -103,10 +170,19 @@ int qw_gpu_group_new_id(void *id_bytes, char *error, size_t error_size) {
     return 1;
 }
 
+static uint32_t env_u32(const char *name, uint32_t fallback) {
+    const char *text = getenv(name);
+    if (!text || !*text) return fallback;
+    long value = strtol(text, NULL, 10);
+    return value > 0 && value < 1000000 ? (uint32_t)value : fallback;
+}
+
 qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int world,
                                 char *error, size_t error_size) {
-    if (!gpu || !id_bytes || world < 1 || rank < 0 || rank >= world) {
-        if (error && error_size) snprintf(error, error_size, "group: bad arguments");
+    if (!gpu || !id_bytes || world < 1 || world > QW_GROUP_MAX_WORLD || rank < 0 ||
+        rank >= world) {
+        if (error && error_size)
+            snprintf(error, error_size, "group: bad arguments (1 to %d ranks)", QW_GROUP_MAX_WORLD);
         return NULL;
     }
     if (!nccl_bind(error, error_size) || !qw_bind(gpu)) return NULL;
@@ -116,6 +192,10 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
     group->rank = rank;
     group->world = world;
     group->sm_count = qwcu_device_sm_count(gpu->device);
+    /* CTAs of the push kernel and the budget of its flag waits (tuning / tests). */
+    group->push_blocks = env_u32("QW_CUDA_GROUP_PUSH_BLOCKS", 32);
+    group->wait_ms = env_u32("QW_CUDA_GROUP_WAIT_MS", 2000);
+    group_layout(group, 1);
     nccl_unique_id id;
     memcpy(&id, id_bytes, sizeof(id));
     int rc = g_nccl.comm_init_rank(&group->comm, world, id, rank);
@@ -125,14 +205,17 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
         free(group);
         return NULL;
     }
+    uint32_t *sync_local = NULL;
     if (cudaMalloc((void **)&group->exchange, QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES + 16) !=
-        cudaSuccess) {
+            cudaSuccess ||
+        cudaMalloc((void **)&sync_local, QW_SYNC_WORDS * sizeof(uint32_t)) != cudaSuccess) {
         if (error && error_size) snprintf(error, error_size, "group: exchange buffer allocation failed");
-        g_nccl.comm_destroy(group->comm);
-        free(group);
+        qw_gpu_group_free(group);
         return NULL;
     }
+    group->sync_peer[rank] = sync_local;
     cudaMemset(group->exchange, 0, QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES + 16);
+    cudaMemset(sync_local, 0, QW_SYNC_WORDS * sizeof(uint32_t));
     int ok = cudaStreamCreateWithFlags(&group->comm_stream, cudaStreamNonBlocking) == cudaSuccess &&
              cudaEventCreateWithFlags(&group->kernel_done, cudaEventDisableTiming) == cudaSuccess;
     for (int b = 0; ok && b < QW_GROUP_MAX_BOUND; b++)
@@ -142,9 +225,34 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
         qw_gpu_group_free(group);
         return NULL;
     }
+    /* Every rank's flag block, mapped everywhere (collective). */
+    if (world > 1 &&
+        !exchange_and_open(group, sync_local, (void **)group->sync_peer, "flag block")) {
+        if (error && error_size) snprintf(error, error_size, "group: %s", h3_gpu_error(gpu));
+        qw_gpu_group_free(group);
+        return NULL;
+    }
     gpu->aux_stream = group->comm_stream;
     return group;
 }
+
+/* Split the ranks into batch_groups x (world / batch_groups) head groups; call it
+ * on every rank with the same value before the first sharded attention.  With 1
+ * (the default) all ranks shard the heads of every batch item. */
+int qw_gpu_group_set_batch_groups(qw_gpu_group *group, int batch_groups) {
+    if (!group) return 0;
+    if (batch_groups < 1 || group->world % batch_groups) {
+        qw_set_error(group->gpu, "group: %d ranks do not split into %d batch groups", group->world,
+                     batch_groups);
+        return 0;
+    }
+    group_layout(group, batch_groups);
+    return 1;
+}
+
+int qw_gpu_group_batch_index(const qw_gpu_group *group) { return group ? group->batch_index : -1; }
+int qw_gpu_group_head_index(const qw_gpu_group *group) { return group ? group->head_index : -1; }
+int qw_gpu_group_head_groups(const qw_gpu_group *group) { return group ? group->head_groups : 0; }
 
 void qw_gpu_group_free(qw_gpu_group *group) {
     if (!group) return;
@@ -158,10 +266,13 @@ void qw_gpu_group_free(qw_gpu_group *group) {
     for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
         if (group->slot_done[b]) cudaEventDestroy(group->slot_done[b]);
     if (group->comm_stream) cudaStreamDestroy(group->comm_stream);
-    for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
-        for (int r = 0; r < group->world && r < QW_GROUP_MAX_WORLD; r++)
+    for (int r = 0; r < group->world && r < QW_GROUP_MAX_WORLD; r++) {
+        for (int b = 0; b < QW_GROUP_MAX_BOUND; b++)
             if (group->peer_out[b][r] && r != group->rank)
                 cudaIpcCloseMemHandle(group->peer_out[b][r]);
+        if (group->sync_peer[r] && r != group->rank) cudaIpcCloseMemHandle(group->sync_peer[r]);
+    }
+    if (group->sync_peer[group->rank]) cudaFree(group->sync_peer[group->rank]);
     if (group->staging) cudaFree(group->staging);
     if (group->exchange) cudaFree(group->exchange);
     if (group->comm) g_nccl.comm_destroy(group->comm);
@@ -185,6 +296,10 @@ int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
         return 0;
     if (!rows || !slice || slice % 8 || slice > UINT32_MAX) {
         qw_set_error(gpu, "head gather: unsupported geometry");
+        return 0;
+    }
+    if (group->batch_groups != 1) {
+        qw_set_error(gpu, "head gather: the NCCL gather spans all ranks; it needs one batch group");
         return 0;
     }
     if (!qw_bind(gpu)) return 0;
@@ -225,9 +340,9 @@ int qw_gpu_group_all_gather_heads_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
 }
 
 /* Map every rank's `full` output buffer into this process (CUDA IPC over the
- * NVLink peer path) so the attention kernel can store its head columns straight
- * into all of them.  Collective: every rank calls it with its own tensor of the
- * same size.  The handles travel through the group's own NCCL communicator. */
+ * NVLink peer path) so the push kernel can store this rank's head columns
+ * straight into all of them.  Collective: every rank calls it with its own tensor
+ * of the same size. */
 int qw_gpu_group_bind_output(qw_gpu_group *group, h3_gpu_tensor *full) {
     if (!group) return 0;
     h3_gpu *gpu = group->gpu;
@@ -235,8 +350,8 @@ int qw_gpu_group_bind_output(qw_gpu_group *group, h3_gpu_tensor *full) {
         qw_set_error(gpu, "group bind: output tensor is absent or not BF16");
         return 0;
     }
-    if (group->world > QW_GROUP_MAX_WORLD) {
-        qw_set_error(gpu, "group bind: at most %d ranks", QW_GROUP_MAX_WORLD);
+    if (gpu->capturing) {
+        qw_set_error(gpu, "group bind: not inside a graph capture");
         return 0;
     }
     if (!qw_bind(gpu)) return 0;
@@ -247,35 +362,10 @@ int qw_gpu_group_bind_output(qw_gpu_group *group, h3_gpu_tensor *full) {
         qw_set_error(gpu, "group bind: at most %d outputs can be bound", QW_GROUP_MAX_BOUND);
         return 0;
     }
-    void **peers = group->peer_out[slot_index];
-    cudaIpcMemHandle_t mine;
-    if (!qw_cuda_ok(gpu, cudaIpcGetMemHandle(&mine, full->dev), "cudaIpcGetMemHandle")) return 0;
-    unsigned char host[QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES];
-    unsigned char *slot = group->exchange + (size_t)group->rank * QW_IPC_HANDLE_BYTES;
-    if (!qw_cuda_ok(gpu, cudaMemcpyAsync(slot, &mine, QW_IPC_HANDLE_BYTES, cudaMemcpyHostToDevice,
-                                         gpu->stream), "handle upload"))
-        return 0;
-    int rc = g_nccl.all_gather(slot, group->exchange, QW_IPC_HANDLE_BYTES, NCCL_UINT8, group->comm,
-                               gpu->stream);
-    if (rc) {
-        qw_set_error(gpu, "ncclAllGather (handles): %s", g_nccl.get_error_string(rc));
-        return 0;
-    }
-    if (!qw_cuda_ok(gpu, cudaMemcpyAsync(host, group->exchange,
-                                         (size_t)group->world * QW_IPC_HANDLE_BYTES,
-                                         cudaMemcpyDeviceToHost, gpu->stream), "handle download") ||
-        !qw_cuda_ok(gpu, cudaStreamSynchronize(gpu->stream), "handle exchange"))
-        return 0;
-    for (int r = 0; r < group->world; r++) {
-        if (r == group->rank) {
-            peers[r] = full->dev;
-            continue;
-        }
-        cudaIpcMemHandle_t theirs;
-        memcpy(&theirs, host + (size_t)r * QW_IPC_HANDLE_BYTES, QW_IPC_HANDLE_BYTES);
-        if (!qw_cuda_ok(gpu, cudaIpcOpenMemHandle(&peers[r], theirs, cudaIpcMemLazyEnablePeerAccess),
-                        "cudaIpcOpenMemHandle"))
-            return 0;
+    if (group->world > 1) {
+        if (!exchange_and_open(group, full->dev, group->peer_out[slot_index], "output")) return 0;
+    } else {
+        group->peer_out[slot_index][0] = full->dev;
     }
     group->bound[slot_index] = full;
     return 1;
@@ -298,15 +388,19 @@ int qw_gpu_group_barrier(qw_gpu_group *group) {
     return 1;
 }
 
-/* Sharded block-causal attention fused with the gather: this rank computes its
- * heads and the kernel's epilogue stores them into head columns
- * [rank*heads_local, (rank+1)*heads_local) of the bound `full` output of EVERY
- * rank (plain stores to peer-mapped memory), then the ranks meet at a barrier.
- * After it, `full` [batch*rows, world*heads_local*128] is complete everywhere. */
+/* Sharded block-causal attention with the gather behind it.  This rank computes
+ * its heads_local heads of its batch group's `batch` items into head columns
+ * [head_index*heads_local, +heads_local) of its own bound `full` output
+ * [batch*rows, head_groups*heads_local*128]; the push kernel then copies that
+ * column slice into every peer's `full` on the communication stream, under
+ * whatever the context's stream runs next.  When the event behind it has passed
+ * (qw_gpu_group_wait_output, or h3_gpu_submit), `full` is complete on this rank.
+ * score_bound may be NULL (running-maximum softmax). */
 int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full,
                                         const h3_gpu_tensor *query, const h3_gpu_tensor *key,
                                         const h3_gpu_tensor *value,
-                                        const h3_gpu_tensor *kv_limit, uint32_t batch,
+                                        const h3_gpu_tensor *kv_limit,
+                                        const h3_gpu_tensor *score_bound, uint32_t batch,
                                         uint32_t rows, uint32_t heads_local,
                                         uint32_t kv_heads_local, uint32_t head_dim,
                                         const uint32_t *text_len, uint32_t text_pad, float scale) {
@@ -320,41 +414,74 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
                           "qw_gpu_group_bind_output");
         return 0;
     }
-    size_t full_count = (size_t)batch * rows * heads_local * head_dim * (size_t)group->world;
+    const uint32_t heads_total = heads_local * (uint32_t)group->head_groups;
+    size_t full_count = (size_t)batch * rows * heads_total * head_dim;
     if (!qw_require_dtype(gpu, full, full_count, H3_GPU_BF16, "group attention output")) return 0;
+    if (score_bound &&
+        !qw_require_dtype(gpu, score_bound, 2, H3_GPU_F32, "group attention score bound"))
+        return 0;
+    if ((uint64_t)batch * rows > UINT32_MAX || (uint64_t)heads_total * head_dim * 2 > UINT32_MAX) {
+        qw_set_error(gpu, "group attention: output too large");
+        return 0;
+    }
     qwcu_attn_args args;
     if (!qw_prepare_block_causal(gpu, &args, NULL, query, key, value, kv_limit, batch, rows,
                                  heads_local, kv_heads_local, head_dim, text_len, text_pad, scale))
         return 0;
     args.out = full->dev;
-    args.n_out_peers = (uint32_t)group->world;
-    for (int r = 0; r < group->world; r++) args.out_peers[r] = group->peer_out[slot_index][r];
-    args.out_heads_total = heads_local * (uint32_t)group->world;
-    args.out_head_offset = heads_local * (uint32_t)group->rank;
-    /* Earlier stores into this output (from any rank) were covered by the barrier
-     * recorded in slot_done; a new round of stores must not start before it. */
-    /* (An event recorded outside the current graph capture belongs to work that is
-     * complete before the graph can run: nothing to wait for.) */
+    args.n_out_peers = 1;
+    args.out_peers[0] = full->dev;
+    args.out_heads_total = heads_total;
+    args.out_head_offset = heads_local * (uint32_t)group->head_index;
+    args.score_bound = score_bound ? (const float *)score_bound->dev : NULL;
+    uint32_t *sync_local = group->sync_peer[group->rank];
+    if (group->n_peers) {
+        args.slot_use = sync_local + QW_SYNC_USE(slot_index);
+        args.n_freed = (uint32_t)group->n_peers;
+        for (int d = 0; d < group->n_peers; d++)
+            args.freed_peer[d] =
+                group->sync_peer[group->peers[d]] + QW_SYNC_FREED(slot_index, group->rank);
+    }
+    /* The previous push out of (and the peers' pushes into) this output must be
+     * over before the kernel overwrites its columns.  (An event recorded outside
+     * the current graph capture belongs to work that is complete before the graph
+     * can run: nothing to wait for.) */
     const uint32_t capture_now = gpu->capturing ? gpu->capture_seq : 0;
     if (group->slot_pending[slot_index] && group->slot_capture[slot_index] == capture_now &&
         !qw_cuda_ok(gpu, cudaStreamWaitEvent(gpu->stream, group->slot_done[slot_index], 0),
                     "group attention (slot wait)"))
         return 0;
     if (!qw_launch_attention(gpu, &args, "group attention")) return 0;
-    if (group->world == 1) return 1;
-    /* The barrier runs on the communication stream, behind this kernel. */
+    if (!group->n_peers) return 1;
     if (!qw_cuda_ok(gpu, cudaEventRecord(group->kernel_done, gpu->stream), "group attention") ||
         !qw_cuda_ok(gpu, cudaStreamWaitEvent(group->comm_stream, group->kernel_done, 0),
                     "group attention"))
         return 0;
-    float *word = (float *)(group->exchange + QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES);
-    int rc = g_nccl.all_reduce(word, word, 1, NCCL_FLOAT32, NCCL_SUM, group->comm,
-                               group->comm_stream);
-    if (rc) {
-        qw_set_error(gpu, "ncclAllReduce (barrier): %s", g_nccl.get_error_string(rc));
-        gpu->chain_failed = 1;
-        return 0;
+    qwcu_push_args push;
+    memset(&push, 0, sizeof(push));
+    push.src = full->dev;
+    push.n_peers = (uint32_t)group->n_peers;
+    push.my_rank = (uint32_t)group->rank;
+    for (int d = 0; d < group->n_peers; d++) {
+        const int peer = group->peers[d];
+        push.dst[d] = group->peer_out[slot_index][peer];
+        push.peer_rank[d] = (uint32_t)peer;
+        push.ready_peer[d] = group->sync_peer[peer] + QW_SYNC_READY(slot_index, group->rank);
     }
+    push.rows = batch * rows;
+    push.row_bytes = heads_total * head_dim * 2;
+    push.col_byte0 = args.out_head_offset * head_dim * 2;
+    push.slice_bytes = heads_local * head_dim * 2;
+    push.slot_use = sync_local + QW_SYNC_USE(slot_index);
+    push.freed_local = sync_local + QW_SYNC_FREED(slot_index, 0);
+    push.ready_local = sync_local + QW_SYNC_READY(slot_index, 0);
+    push.arrivals = sync_local + QW_SYNC_ARRIVALS(slot_index);
+    push.status = gpu->status_dev;
+    push.wait_ms = group->wait_ms;
+    push.max_blocks = group->push_blocks;
+    int rc = qwcu_push_launch(&push, group->comm_stream);
+    qw_count_launch(gpu, rc, "head push");
+    if (rc) return 0;
     if (!qw_cuda_ok(gpu, cudaEventRecord(group->slot_done[slot_index], group->comm_stream),
                     "group attention"))
         return 0;
@@ -364,9 +491,9 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
 }
 
 /* Make the context's stream wait until `full` (a bound output) is complete on
- * this rank, i.e. until the barrier behind the last fused gather into it has
- * passed.  Call it before enqueueing a consumer of `full`; h3_gpu_submit waits
- * for every outstanding barrier by itself. */
+ * this rank, i.e. until the push behind the last sharded attention into it has
+ * seen every peer's columns land.  Call it before enqueueing a consumer of
+ * `full`; h3_gpu_submit waits for every outstanding push by itself. */
 int qw_gpu_group_wait_output(qw_gpu_group *group, const h3_gpu_tensor *full) {
     if (!group) return 0;
     h3_gpu *gpu = group->gpu;

@@ -12,7 +12,7 @@
 #include "qwen_attn_host.h"
 #include "qwen_gpu_ext.h"
 
-enum { QW_ATTN_SM100 = 0, QW_ATTN_SCALAR = 1, QW_ATTN_SM100_WHOLE = 2 };
+enum { QW_ATTN_SM100 = 0, QW_ATTN_SCALAR = 1, QW_ATTN_SM100_WHOLE = 2, QW_ATTN_SM100_ROW = 3 };
 
 struct h3_gpu {
     int device;
@@ -34,6 +34,10 @@ struct h3_gpu {
     int capturing;
     uint32_t capture_seq;      /* identifies the capture an event was recorded in */
     uint64_t capture_launches; /* kernel launches counted since capture began */
+    /* Copy lanes beside the compute stream (qw_gpu_fence, qw_gpu_tensor_*_lane):
+     * lane 0 is `stream`, lanes 1.. are created on first use; submit joins them. */
+    cudaStream_t lane[3];
+    cudaEvent_t lane_event;
     /* Scratch for the pre-scaled query of the h3 causal variant; grows on demand. */
     void *scratch;
     size_t scratch_bytes;

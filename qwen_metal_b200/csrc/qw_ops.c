@@ -322,6 +322,7 @@ int qw_launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what) {
     if (!qw_bind(gpu)) return 0;
     args->status = gpu->status_dev;
     args->whole_units = gpu->attn_kernel == QW_ATTN_SM100_WHOLE;
+    args->row_softmax = gpu->attn_kernel == QW_ATTN_SM100_ROW;
     int scalar = gpu->attn_kernel == QW_ATTN_SCALAR;
     /* Degenerate scales cannot ride the exp2-domain fast path. */
     if (!(args->scale > 0.0f) || !isfinite(args->scale)) scalar = 1;

@@ -142,9 +142,12 @@ class LayerRunner:
     """Device-resident state of one workload and the per-layer op sequence."""
 
     def __init__(self, gpu: abi.Gpu, w: Workload, heads_local: int | None = None,
-                 bounded: bool | None = None):
+                 bounded: bool | None = None, batch_items: tuple | None = None):
+        """heads_local / batch_items = (first, count): this rank's share when the
+        heads and the batch items are sharded over several GPUs."""
         self.gpu, self.w = gpu, w
         self.heads = heads_local or w.heads
+        self.batch0, self.batch = batch_items or (0, w.batch)
         # With the QK-norm in front, the prologue also leaves the norm bounds of its
         # outputs on the device and the attention kernel runs its fixed-exponent
         # softmax; QW_SOFTMAX=max (or bounded=False) keeps the running-maximum path.
@@ -152,48 +155,51 @@ class LayerRunner:
             bounded = os.environ.get("QW_SOFTMAX", "bounded") != "max"
         self.bounded = bool(bounded and w.prologue)
         self.bound = gpu.new_f32(2) if self.bounded else None
-        n = w.batch * w.rows * self.heads * HEAD_DIM
+        n = self.batch * w.rows * self.heads * HEAD_DIM
         self.n = n
         self.limits_host = w.limits()
         self.limits = gpu.u32(self.limits_host)
         if w.prologue:
             cos, sin = w.rope_tables()
             self.cos, self.sin = gpu.f32(cos), gpu.f32(sin)
-        self.text_len = (np.asarray(w.text_len, dtype=np.uint32) if w.text_pad else None)
+        self.text_len = (np.asarray(w.text_len[self.batch0:self.batch0 + self.batch],
+                                    dtype=np.uint32) if w.text_pad else None)
         self.out = gpu.new_bf16(n)
 
     def enqueue(self, q, k, v, wq=None, wk=None, out=None, q_work=None, k_work=None,
                 group=None, full=None):
         """One layer: [fused QK-norm + RoPE] then block-causal attention.  With
         q_work/k_work the prologue writes there and leaves q, k untouched.  With a
-        multi-GPU group and a bound `full` output the attention kernel stores this
-        rank's heads into every rank's `full` (fused gather)."""
+        multi-GPU group and a bound `full` output the kernel writes this rank's head
+        columns of `full` and the group's push kernel copies them to the peers."""
         g, w, lib = self.gpu, self.w, self.gpu.lib
+        batch = self.batch
         out = out or self.out
         if w.prologue:
             qo, ko = (q_work or q), (k_work or k)
             if self.bounded:
                 g.check(lib.qw_gpu_qk_norm_rope_bound_bf16(
-                    g.handle, qo, ko, q, k, wq, wk, self.cos, self.sin, self.bound, w.batch,
+                    g.handle, qo, ko, q, k, wq, wk, self.cos, self.sin, self.bound, batch,
                     w.rows, self.heads, HEAD_DIM, EPS), "qk_norm_rope_bound")
             else:
                 g.check(lib.qw_gpu_qk_norm_rope_out_bf16(g.handle, qo, ko, q, k, wq, wk, self.cos,
-                                                         self.sin, w.batch, w.rows, self.heads,
+                                                         self.sin, batch, w.rows, self.heads,
                                                          HEAD_DIM, EPS),
                         "qk_norm_rope")
             q, k = qo, ko
         tl = abi._ptr(self.text_len) if self.text_len is not None else None
         if group is not None:
             g.check(lib.qw_gpu_group_attn_block_causal_bf16(
-                group, full, q, k, v, self.limits, w.batch, w.rows, self.heads, self.heads,
-                HEAD_DIM, tl, w.text_pad, SCALE), "group_attn_block_causal")
+                group, full, q, k, v, self.limits, self.bound if self.bounded else None, batch,
+                w.rows, self.heads, self.heads, HEAD_DIM, tl, w.text_pad, SCALE),
+                "group_attn_block_causal")
             return full
         if self.bounded:
             g.check(lib.qw_gpu_attn_block_causal_bounded_bf16(
-                g.handle, out, q, k, v, self.limits, self.bound, w.batch, w.rows, self.heads,
+                g.handle, out, q, k, v, self.limits, self.bound, batch, w.rows, self.heads,
                 self.heads, HEAD_DIM, tl, w.text_pad, SCALE), "attn_block_causal_bounded")
             return out
-        g.check(lib.qw_gpu_attn_block_causal_bf16(g.handle, out, q, k, v, self.limits, w.batch,
+        g.check(lib.qw_gpu_attn_block_causal_bf16(g.handle, out, q, k, v, self.limits, batch,
                                                   w.rows, self.heads, self.heads, HEAD_DIM, tl,
                                                   w.text_pad, SCALE),
                 "attn_block_causal")

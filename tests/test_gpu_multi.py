@@ -1,5 +1,6 @@
 """GPU, needs >= 2 devices: head-sharded attention across one process per GPU
-(NCCL gather and the fused peer-store gather) against the CPU oracle.  Skipped on
+(NCCL gather and the push gather, heads over all ranks and batch items split
+first), every rank's full gathered output against the CPU oracle.  Skipped on
 a single-GPU box.  NVLS is switched off for NCCL so a rank that fails cannot take
 multicast-bound memory of the others with it."""
 import os
@@ -20,7 +21,7 @@ def device_count():
         return 0
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_attention_world(tmp_path, world):
     if device_count() < world:
         pytest.skip(f"needs {world} GPUs")

@@ -255,7 +255,7 @@ def test_cfg1_bidirectional_text_reading(gpu):
     gates(out, oracle_layer(w, inputs), "cfg1 bidirectional text")
 
 
-@pytest.fixture(params=["sm100", "sm100-whole"])
+@pytest.fixture(params=["sm100", "sm100-whole", "sm100-row"])
 def tail_form(request, gpu):
     assert gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, request.param.encode())
     yield request.param
@@ -593,6 +593,35 @@ def test_range_copies_move_the_bytes(gpu):
     assert np.array_equal(gpu.read_bf16(s16, 1000), src16)  # the source is untouched
     for t in (s16, d16, s32, d32):
         gpu.free(t)
+
+
+def test_copy_lanes_order_uploads_compute_and_readbacks(gpu):
+    """Upload on lane 1, an op on the context's stream, read-back on lane 2, joined by
+    fences: the bytes arrive in order, and h3_gpu_submit waits for every lane."""
+    lib = gpu.lib
+    n = 1 << 20
+    rng = np.random.default_rng(12)
+    src = rng.integers(0, 1 << 16, n).astype(np.uint16)
+    host_in, host_out = lib.qw_gpu_host_alloc(n * 2), lib.qw_gpu_host_alloc(n * 2)
+    assert host_in and host_out
+    C.memmove(host_in, src.ctypes.data, n * 2)
+    C.memset(host_out, 0, n * 2)
+    a, b = gpu.new_bf16(n), gpu.new_bf16(n)
+    gpu.begin()
+    for _ in range(3):  # re-used buffers: each round must see the previous one finished
+        gpu.check(lib.qw_gpu_fence(gpu.handle, 0, 1), "fence")      # a was read by the copy
+        gpu.check(lib.qw_gpu_tensor_write_lane(gpu.handle, a, host_in, n, 1), "upload")
+        gpu.check(lib.qw_gpu_fence(gpu.handle, 1, 0), "fence")
+        gpu.check(lib.qw_gpu_fence(gpu.handle, 2, 0), "fence")      # b was read back
+        gpu.check(lib.h3_gpu_copy_bf16(gpu.handle, b, 0, a, 0, n), "copy")
+        gpu.check(lib.qw_gpu_fence(gpu.handle, 0, 2), "fence")
+        gpu.check(lib.qw_gpu_tensor_read_lane(gpu.handle, b, host_out, n, 2), "read-back")
+    gpu.submit()
+    got = np.frombuffer(C.string_at(host_out, n * 2), np.uint16)
+    assert np.array_equal(got, src)
+    assert lib.qw_gpu_fence(gpu.handle, 0, 7) == 0 and "no such lane" in gpu.error()
+    lib.qw_gpu_host_free(host_in), lib.qw_gpu_host_free(host_out)
+    gpu.free(a), gpu.free(b)
 
 
 def test_scratch_cannot_grow_inside_a_graph_capture(gpu):
