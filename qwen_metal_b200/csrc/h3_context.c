@@ -580,7 +580,12 @@ int qw_gpu_graph_begin(h3_gpu *gpu) {
 
 qw_gpu_graph *qw_gpu_graph_end(h3_gpu *gpu) {
     if (!gpu || !gpu->capturing || !qw_bind(gpu)) return NULL;
-    if (gpu->aux_stream) { /* join the communication stream back into the capture */
+    /* Join the communication stream back into the capture, if this capture forked
+     * into it at all (a capturing stream must not wait on an event of a stream that
+     * is not part of the capture). */
+    enum cudaStreamCaptureStatus aux_status = cudaStreamCaptureStatusNone;
+    if (gpu->aux_stream && cudaStreamIsCapturing(gpu->aux_stream, &aux_status) == cudaSuccess &&
+        aux_status == cudaStreamCaptureStatusActive) {
         if (!gpu->aux_joined) cudaEventCreateWithFlags(&gpu->aux_joined, cudaEventDisableTiming);
         if (gpu->aux_joined && cudaEventRecord(gpu->aux_joined, gpu->aux_stream) == cudaSuccess)
             cudaStreamWaitEvent(gpu->stream, gpu->aux_joined, 0);

@@ -76,6 +76,7 @@ static int nccl_bind(char *error, size_t error_size) {
  *   [8, 40)   freed[slot][r]   written by rank r: its slot may be stored into
  *   [40, 72)  ready[slot][r]   written by rank r: its columns have landed here */
 #define QW_SYNC_WORDS 128
+#define QW_SYNC_BLOCK_BYTES ((size_t)4 << 20)
 #define QW_SYNC_USE(slot) (slot)
 #define QW_SYNC_ARRIVALS(slot) (4 + (slot))
 #define QW_SYNC_FREED(slot, r) (8 + (slot) * QW_GROUP_MAX_WORLD + (r))
@@ -208,7 +209,9 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
     uint32_t *sync_local = NULL;
     if (cudaMalloc((void **)&group->exchange, QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES + 16) !=
             cudaSuccess ||
-        cudaMalloc((void **)&sync_local, QW_SYNC_WORDS * sizeof(uint32_t)) != cudaSuccess) {
+        /* (an allocation of its own: small ones share a block, and a block can be
+         * opened through IPC only once per process) */
+        cudaMalloc((void **)&sync_local, QW_SYNC_BLOCK_BYTES) != cudaSuccess) {
         if (error && error_size) snprintf(error, error_size, "group: exchange buffer allocation failed");
         qw_gpu_group_free(group);
         return NULL;

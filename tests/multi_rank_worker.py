@@ -86,7 +86,9 @@ def main():
 
         # (b) push gather: four layers alternating between two bound outputs, then
         # two layers replayed from a captured graph
-        full_b = [gpu.new_bf16(full_count) for _ in range(2)]
+        # (allocations of a few MB each: smaller ones may share a device memory block,
+        # and a block can be opened through CUDA IPC only once per process)
+        full_b = [gpu.new_bf16(max(full_count, 1 << 22)) for _ in range(2)]
         for t in full_b:
             gpu.check(lib.qw_gpu_group_bind_output(group, t), "bind")
 
