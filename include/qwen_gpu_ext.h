@@ -196,6 +196,13 @@ int qw_gpu_tensor_read_lane(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *host
  * keeps one thread per query row instead of pairing the warpgroups on each
  * sub-tile) or "scalar" (diagnostic fp32 kernel).  Returns 0 on an unknown name. */
 int qw_gpu_set_attention_kernel(h3_gpu *gpu, const char *name);
+/* Test hook for the attention kernel's bounded waits: later launches use a wait
+ * budget of wait_cycles SM cycles and their TMA producer leaves out every key tile
+ * from visited tile withhold_from_tile (>= 1) on; the waits behind the missing
+ * tile run out, every role of the CTA leaves through its clean exit (loads
+ * drained, TMEM freed) and h3_gpu_submit returns 0 with the place of the first
+ * expiry.  (0, 0) restores normal operation. */
+int qw_gpu_debug_attention_waits(h3_gpu *gpu, long long wait_cycles, int withhold_from_tile);
 /* Launches enqueued by this context's ops since creation (own kernels only). */
 uint64_t qw_gpu_kernel_launches(const h3_gpu *gpu);
 

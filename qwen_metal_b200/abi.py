@@ -125,6 +125,7 @@ _SIGNATURES = {
     "qw_gpu_tensor_read_lane": (C.c_int, [c_gpu, c_tensor, C.c_void_p, size_t, C.c_int]),
     "qw_gpu_set_attention_kernel": (C.c_int, [c_gpu, C.c_char_p]),
     "qw_gpu_kernel_launches": (C.c_uint64, [c_gpu]),
+    "qw_gpu_debug_attention_waits": (C.c_int, [c_gpu, C.c_longlong, C.c_int]),
     "qw_gpu_graph_begin": (C.c_int, [c_gpu]),
     "qw_gpu_graph_end": (C.c_void_p, [c_gpu]),
     "qw_gpu_graph_launch": (C.c_int, [c_gpu, C.c_void_p]),

@@ -98,6 +98,7 @@ struct __align__(16) SharedControl {
     unsigned long long bars[kBarCount];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
+    long long wait_cycles;  // budget of every bounded wait of this CTA
     int n_tiles[2];      // key tiles each sub-tile needs (by its largest limit)
     int warp_max[8];     // per softmax warp: largest limit
     int skip_lo, skip_hi;  // key tiles [skip_lo, skip_hi) lie inside the padding window
@@ -148,6 +149,11 @@ struct KernelParams {
     uint32_t *slot_use;
     uint32_t *freed_peer[8];
     uint32_t n_freed;
+    // Bounded-wait exercise (tests only): budget in SM cycles (0 = the default) and
+    // the first visited key tile the producer does NOT load (< 0: loads everything),
+    // so that the waits downstream of it run out and the CTA takes its clean exit.
+    long long wait_cycles;
+    int withhold_from;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -198,7 +204,7 @@ __device__ __forceinline__ bool mbar_wait_slow(SharedControl *ctl, unsigned long
         for (int i = 0; i < 32; ++i)
             if (mbar_try(bar, parity)) return true;
         if (ctl->abort_flag) return false;
-        if (clock64() - start > kWaitCycles) {
+        if (clock64() - start > ctl->wait_cycles) {
             ctl->abort_flag = 1;
             if (atomicCAS(status, 0u, (uint32_t)QWCU_STATUS_WAIT_TIMEOUT) == 0u) {
                 status[1] = where;
@@ -1251,6 +1257,10 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
     const int col = (int)(kvh * kHeadDim);
     // One (K, V) pair of visited tile u into the next two ring slots.
     auto load_pair = [&](int u) {
+        if (p.withhold_from >= 0 && u >= p.withhold_from) {
+            ok = false;  // the tile stays away: nothing is issued, nothing is in flight
+            return;
+        }
         const int j = phys_tile(ctl, u);
         for (int which = 0; which < 2 && ok; ++which) {
             uint32_t slot = t % kStages, par = ((t / kStages) & 1u) ^ 1u;
@@ -1284,7 +1294,7 @@ __device__ void tma_role(const KernelParams &p, SharedControl *ctl, uint8_t *sme
         uint32_t slot = u % kStages, par = (u / kStages) & 1u;
         long long start = clock64();
         while (!mbar_try(&ctl->bars[kBarKvFull + slot], par))
-            if (clock64() - start > kWaitCycles) break;
+            if (clock64() - start > ctl->wait_cycles) break;
     }
 }
 
@@ -1348,6 +1358,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
         mbar_init(&ctl->bars[kBarMerge], kTileM / 32);
         mbar_init(&ctl->bars[kBarDebug], 1);
         ctl->abort_flag = 0;
+        ctl->wait_cycles = p.wait_cycles > 0 ? p.wait_cycles : kWaitCycles;
         int lo = 0, hi = 0;
         if (p.text_pad && p.text_len[b] < p.text_pad) {
             lo = ((int)p.text_len[b] + kTileN - 1) / kTileN;
@@ -1474,7 +1485,7 @@ qw_attn_sm100_kernel(const __grid_constant__ CUtensorMap map_q,
             if (row0 + (uint32_t)i * kTileM >= p.q_rows) continue;
             long long start = clock64();
             while (!mbar_try(&ctl->bars[kBarQFull + i], 0))
-                if (clock64() - start > kWaitCycles) break;
+                if (clock64() - start > ctl->wait_cycles) break;
         }
     }
 
@@ -1687,6 +1698,8 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
         p.out_heads_total = a->heads;
         p.out_head_offset = 0;
     }
+    p.wait_cycles = a->wait_cycles;
+    p.withhold_from = a->withhold_from > 0 ? a->withhold_from : -1;
     p.slot_use = a->slot_use;
     p.n_freed = a->slot_use ? a->n_freed : 0;
     if (p.n_freed > 8) return (int)cudaErrorInvalidValue;

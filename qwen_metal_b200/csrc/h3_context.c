@@ -397,6 +397,18 @@ int qw_gpu_tensor_read_async(h3_gpu *gpu, const h3_gpu_tensor *tensor, void *hos
                       "asynchronous tensor read");
 }
 
+/* Exercise of the attention kernel's bounded waits (tests): the next launches
+ * run with a wait budget of `wait_cycles` SM cycles and their producer leaves out
+ * every key tile from visited tile `withhold_from_tile` (>= 1) on, so the waits
+ * behind it run out: the kernel records where, exits cleanly and h3_gpu_submit
+ * returns 0 with the message.  (0, 0) restores normal operation. */
+int qw_gpu_debug_attention_waits(h3_gpu *gpu, long long wait_cycles, int withhold_from_tile) {
+    if (!gpu || wait_cycles < 0 || withhold_from_tile < 0) return 0;
+    gpu->attn_wait_cycles = wait_cycles;
+    gpu->attn_withhold_tile = withhold_from_tile;
+    return 1;
+}
+
 /* ---- copy lanes (no counterpart in the reference) -------------------------
  * A host program that streams inputs in and results out overlaps three things:
  * the upload of the next layer, the compute of this one, the read-back of the

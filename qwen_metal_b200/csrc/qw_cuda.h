@@ -85,6 +85,12 @@ typedef struct {
     /* sm100 kernel with a score bound: one thread per query row (one warpgroup per
      * sub-tile) instead of both warpgroups sharing each sub-tile's keys. */
     int row_softmax;
+    /* Bounded-wait exercise (sm100 kernel, tests only): wait budget in SM cycles
+     * (0 = default, about 0.2 s) and the first visited key tile (>= 1) that the TMA
+     * producer does not load (0 = none withheld): the waits behind it run out, the
+     * CTA records where, drains, frees its TMEM and returns. */
+    long long wait_cycles;
+    int withhold_from;
 } qwcu_attn_args;
 
 /* tcgen05/TMEM/TMA flash-attention forward (sm_100a). */

@@ -194,7 +194,7 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
     group->world = world;
     group->sm_count = qwcu_device_sm_count(gpu->device);
     /* CTAs of the push kernel and the budget of its flag waits (tuning / tests). */
-    group->push_blocks = env_u32("QW_CUDA_GROUP_PUSH_BLOCKS", 32);
+    group->push_blocks = env_u32("QW_CUDA_GROUP_PUSH_BLOCKS", 128);
     group->wait_ms = env_u32("QW_CUDA_GROUP_WAIT_MS", 2000);
     group_layout(group, 1);
     nccl_unique_id id;

@@ -27,6 +27,8 @@ struct h3_gpu {
     uint32_t *status_dev;  /* QWCU_STATUS_WORDS words, zero when healthy */
     uint32_t *status_host; /* pinned mirror */
     int attn_kernel;
+    long long attn_wait_cycles; /* tests: budget of the attention kernel's waits (0 = default) */
+    int attn_withhold_tile;     /* tests: first key tile the producer leaves out (0 = none) */
     /* A multi-GPU group's communication stream; submit waits for it too. */
     cudaStream_t aux_stream;
     cudaEvent_t aux_joined;

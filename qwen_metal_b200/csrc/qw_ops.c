@@ -323,6 +323,8 @@ int qw_launch_attention(h3_gpu *gpu, qwcu_attn_args *args, const char *what) {
     args->status = gpu->status_dev;
     args->whole_units = gpu->attn_kernel == QW_ATTN_SM100_WHOLE;
     args->row_softmax = gpu->attn_kernel == QW_ATTN_SM100_ROW;
+    args->wait_cycles = gpu->attn_wait_cycles;
+    args->withhold_from = gpu->attn_withhold_tile;
     int scalar = gpu->attn_kernel == QW_ATTN_SCALAR;
     /* Degenerate scales cannot ride the exp2-domain fast path. */
     if (!(args->scale > 0.0f) || !isfinite(args->scale)) scalar = 1;

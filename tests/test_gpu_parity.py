@@ -624,6 +624,45 @@ def test_copy_lanes_order_uploads_compute_and_readbacks(gpu):
     gpu.free(a), gpu.free(b)
 
 
+@pytest.mark.parametrize("softmax", ["max", "bounded"])
+@pytest.mark.parametrize("form", ["sm100", "sm100-whole", "sm100-row"])
+def test_bounded_waits_run_out_cleanly(gpu, form, softmax):
+    """Every device-side wait of the attention kernel has a budget.  With a short
+    budget and a producer that leaves out every key tile from the third on, the
+    waits behind the missing tile run out: the CTAs record where, drain, free their
+    TMEM and return; h3_gpu_submit reports it; and the very next launch on the same
+    context computes the right answer (nothing hung, nothing leaked)."""
+    lib = gpu.lib
+    rng = np.random.default_rng(31)
+    S, H = 1024, 3
+    q, k, v = (randn_bf16(rng, (1, S, H, 128)) for _ in range(3))
+    limits = O.prefix_limits([(100, 0), (S - 100, 1)])
+    qt, kt, vt, lt, ot = gpu.bf16(q), gpu.bf16(k), gpu.bf16(v), gpu.u32(limits), gpu.new_bf16(q.size)
+    bt = gpu.f32(np.array([14.0, 14.0], np.float32))  # N(0,1) rows: norms ~ 11.3 +- 0.7
+    assert lib.qw_gpu_set_attention_kernel(gpu.handle, form.encode())
+
+    def launch():
+        if softmax == "bounded":
+            return lib.qw_gpu_attn_block_causal_bounded_bf16(
+                gpu.handle, ot, qt, kt, vt, lt, bt, 1, S, H, H, 128, None, 0, SCALE)
+        return lib.qw_gpu_attn_block_causal_bf16(gpu.handle, ot, qt, kt, vt, lt, 1, S, H, H, 128,
+                                                 None, 0, SCALE)
+
+    assert lib.qw_gpu_debug_attention_waits(gpu.handle, 2_000_000, 2)   # ~1 ms per wait
+    gpu.begin()
+    assert launch() == 1                      # the launch itself is fine ...
+    assert lib.h3_gpu_submit(gpu.handle) == 0  # ... the kernel reports the expired wait
+    assert "wait ran out" in gpu.error(), gpu.error()
+    assert lib.qw_gpu_debug_attention_waits(gpu.handle, 0, 0)
+    gpu.begin()
+    gpu.check(launch(), "attention after the expired waits")
+    gpu.submit()
+    ref, _ = O.sdpa(q, k, v, limits, 1, S, S, H, H, SCALE)
+    gates(gpu.read_bf16(ot, q.size), ref, f"after expired waits ({form}, {softmax})")
+    for t in (qt, kt, vt, lt, ot, bt):
+        gpu.free(t)
+
+
 def test_scratch_cannot_grow_inside_a_graph_capture(gpu):
     """The h3 causal op keeps its pre-scaled query in scratch that the context
     caches.  Inside a graph capture that block may be reused but not created or
