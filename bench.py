@@ -658,7 +658,39 @@ def neighbour_rooflines(ctx, job, peaks):
     gate_s = ctx.timed(gate_only, 5) / 20
     n = job.n_local
     gpu.free(modulation), gpu.free(row_map)
+    # the projections either side of the path on this workload's activations:
+    # [batch*rows, H*128] x three [H*128, H*128] weights, and the output projection
+    wts = [gpu.bf16(workloads.normal_bf16(rng, (width, width), 0.0, width ** -0.5)) for _ in range(3)]
+    outs = [gpu.new_bf16(rows_all * width) for _ in range(3)]
+    x = acts[0]
+
+    def qkv_only():
+        gpu.check(lib.qw_gpu_qkv_bf16(gpu.handle, *outs, x, *wts, rows_all, width), "qkv")
+
+    def qkv_fused():
+        _, _, _, wqt, wkt = job.layers[0]
+        gpu.check(lib.qw_gpu_qkv_norm_rope_bf16(gpu.handle, *outs, x, *wts, wqt, wkt, job.runner.cos,
+                                                job.runner.sin, None, w.batch, w.rows, width, 1e-6),
+                  "qkv fused")
+
+    def out_proj():
+        gpu.check(lib.h3_gpu_linear_bf16(gpu.handle, outs[0], x, wts[0], None, rows_all, width,
+                                         width), "linear")
+
+    gemms = {}
+    for name, fn, mult in (("qkv_projection", qkv_only, 3), ("qkv_projection_norm_rope", qkv_fused, 3),
+                           ("output_projection", out_proj, 1)):
+        ctx.timed(fn, 2)
+        s_ = ctx.timed(fn, 10) / 10
+        flops = 2.0 * rows_all * width * width * mult
+        gemms[name] = {"kernel": "qw_linear_sm100_kernel", "bound": "tensor",
+                       "flops_per_launch": flops, "achieved": flops / s_ / 1e12, "unit": "TFLOP/s",
+                       "peak": peaks["bf16"], "frac": flops / s_ / 1e12 / peaks["bf16"],
+                       "launch_ms": s_ * 1e3, "shape": [rows_all, width, width * mult]}
+    for t in wts + outs:
+        gpu.free(t)
     return {
+        **gemms,
         "layer_norm_mod": {"bound": "hbm", "bytes_per_launch": 2 * n * 2,
                            "achieved": 2 * n * 2 / norm_s / 1e9, "unit": "GB/s",
                            "frac": 2 * n * 2 / norm_s / 1e9 / peaks["hbm"],

@@ -133,6 +133,15 @@ int h3_gpu_sdpa_bf16_head_major_output(h3_gpu *gpu, h3_gpu_tensor *output,
                                        const h3_gpu_tensor *value, uint32_t sequence,
                                        uint32_t heads, uint32_t head_dim, float scale);
 
+/* reference h3_gpu.h:293-299, h3_gpu.m:2697-2812, h3_shaders.metal:788-822: bf16
+ * linear layer, output[rows, output_dim] = bf16(bias + input . weight^T) with the
+ * weight in its [output_dim, input_dim] checkpoint layout, fp32 accumulation;
+ * bias may be NULL.  The DiT block's output projection behind the attention
+ * (qwen_dit.m:1446).  Dimensions must be multiples of 8. */
+int h3_gpu_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                       const h3_gpu_tensor *weight, const h3_gpu_tensor *bias, uint32_t rows,
+                       uint32_t input_dim, uint32_t output_dim);
+
 /* reference h3_gpu.h:527-530, h3_gpu.m:4478-4493, h3_shaders.metal:4309-4329:
  * in-place per-(row, head) RMSNorm, single bf16 rounding of x*inv*w. */
 int h3_gpu_head_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *tensor, const h3_gpu_tensor *weight,

@@ -40,6 +40,14 @@ int qw_gpu_head_rms_norm_bf16(h3_gpu *gpu, h3_gpu_tensor *tensor, const h3_gpu_t
                               uint32_t sequence, uint32_t heads, uint32_t head_dim,
                               float epsilon);
 
+/* reference qwen_gpu_ext.h:202-210, h3_gpu.m:2918-3018: fused q/k/v projection in
+ * front of the attention (qwen_dit.m:1270), three [dim, dim] weights in their
+ * [out, in] layout sharing the input, one launch. */
+int qw_gpu_qkv_bf16(h3_gpu *gpu, h3_gpu_tensor *query_out, h3_gpu_tensor *key_out,
+                    h3_gpu_tensor *value_out, const h3_gpu_tensor *input,
+                    const h3_gpu_tensor *query_weight, const h3_gpu_tensor *key_weight,
+                    const h3_gpu_tensor *value_weight, uint32_t rows, uint32_t dim);
+
 /* reference qwen_gpu_ext.h:116-123, h3_gpu.m:5745-5789: flash SDPA, every query
  * row sees every key; q_rows may differ from kv_rows. */
 int qw_gpu_flash_sdpa_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *query,
@@ -111,6 +119,22 @@ int qw_gpu_qk_norm_rope_bound_bf16(h3_gpu *gpu, h3_gpu_tensor *query_output,
                                    h3_gpu_tensor *score_bound, uint32_t batch,
                                    uint32_t sequence, uint32_t heads, uint32_t head_dim,
                                    float epsilon);
+
+/* NEW: the q/k/v projection with the per-head QK RMSNorm and the interleaved RoPE
+ * in the GEMM's epilogue: the reference's sequence qw_gpu_qkv_bf16, two
+ * h3_gpu_head_rms_norm_bf16, qw_gpu_qk_rope_bf16 (qwen_dit.m:1270-1278) as one
+ * launch, with the same bf16 roundings between the stages.  input [batch*sequence,
+ * dim]; tables f32 [sequence, 64]; dim a multiple of 128 (whole heads).
+ * score_bound (F32 tensor >= 2 elements, or NULL) as in
+ * qw_gpu_qk_norm_rope_bound_bf16. */
+int qw_gpu_qkv_norm_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query_out, h3_gpu_tensor *key_out,
+                              h3_gpu_tensor *value_out, const h3_gpu_tensor *input,
+                              const h3_gpu_tensor *query_weight, const h3_gpu_tensor *key_weight,
+                              const h3_gpu_tensor *value_weight,
+                              const h3_gpu_tensor *norm_weight_q,
+                              const h3_gpu_tensor *norm_weight_k, const h3_gpu_tensor *rope_cos,
+                              const h3_gpu_tensor *rope_sin, h3_gpu_tensor *score_bound,
+                              uint32_t batch, uint32_t sequence, uint32_t dim, float epsilon);
 
 /* NEW: the prologue of a target-only layer of the edit path, where only the
  * target image rows are recomputed against the per-layer K/V cache of an

@@ -320,6 +320,34 @@ void qwo_gate_bf16(uint16_t *out, const uint16_t *residual, const uint16_t *bran
     }
 }
 
+/* h3_shaders.metal:788-822 */
+void qwo_linear_bf16(uint16_t *out, const uint16_t *in, const uint16_t *weight,
+                     const uint16_t *bias, uint32_t rows, uint32_t input_dim,
+                     uint32_t output_dim, const uint32_t *row_index, size_t n_rows) {
+    const int64_t count = row_index ? (int64_t)n_rows : (int64_t)rows;
+    /* the weights as floats once: every row reuses them */
+    float *wf = malloc((size_t)output_dim * input_dim * sizeof(float));
+    if (!wf) return;
+    for (size_t i = 0; i < (size_t)output_dim * input_dim; i++) wf[i] = qwo_bf16_to_f32(weight[i]);
+#pragma omp parallel for schedule(dynamic, 4)
+    for (int64_t n = 0; n < count; n++) {
+        const uint32_t row = row_index ? row_index[n] : (uint32_t)n;
+        if (row >= rows) continue;
+        float *x = malloc(input_dim * sizeof(float));
+        if (!x) continue;
+        for (uint32_t k = 0; k < input_dim; k++)
+            x[k] = qwo_bf16_to_f32(in[(size_t)row * input_dim + k]);
+        for (uint32_t c = 0; c < output_dim; c++) {
+            float sum = bias ? qwo_bf16_to_f32(bias[c]) : 0.0f;
+            const float *w = wf + (size_t)c * input_dim;
+            for (uint32_t k = 0; k < input_dim; k++) sum = fmaf(x[k], w[k], sum);
+            out[(size_t)row * output_dim + c] = qwo_f32_to_bf16(sum);
+        }
+        free(x);
+    }
+    free(wf);
+}
+
 /* tests/test_prefix_kernel.c:72-97, one (batch,row): all heads. */
 static uint64_t sdpa_row(float *out, const uint16_t *q, const uint16_t *k,
                          const uint16_t *v, uint32_t b, uint32_t r, uint32_t limit,

@@ -132,6 +132,14 @@ void qwo_gate_bf16(uint16_t *out, const uint16_t *residual, const uint16_t *bran
                    const uint16_t *modulation, const uint32_t *row_map, uint32_t rows,
                    uint32_t width, uint32_t slots, uint32_t gate_slot);
 
+/* bf16 linear layer: out[r][c] = bf16(bias[c] + sum_k in[r][k] * w[c][k]), fp32,
+ * a serial fma chain over k that starts from the bias (h3_shaders.metal:788-822;
+ * weight in its [out, in] layout).  bias may be NULL.  row_index == NULL computes
+ * every row; otherwise only the n_rows listed rows are computed and written. */
+void qwo_linear_bf16(uint16_t *out, const uint16_t *in, const uint16_t *weight,
+                     const uint16_t *bias, uint32_t rows, uint32_t input_dim,
+                     uint32_t output_dim, const uint32_t *row_index, size_t n_rows);
+
 /* OpenMP threads the loops above use; qwo_set_threads overrides the environment
  * (a launcher may export OMP_NUM_THREADS=1 to every rank). */
 void qwo_set_threads(int threads);

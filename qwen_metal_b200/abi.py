@@ -78,6 +78,9 @@ _SIGNATURES = {
     "h3_gpu_sdpa_bf16_head_major_output": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, f32]),
     "h3_gpu_head_rms_norm_bf16": (C.c_int, [c_gpu, c_tensor, c_tensor, u32, u32, u32, f32]),
+    "h3_gpu_linear_bf16": (C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32]),
+    "qw_gpu_qkv_bf16": (C.c_int, [c_gpu] + [c_tensor] * 7 + [u32, u32]),
+    "qw_gpu_qkv_norm_rope_bf16": (C.c_int, [c_gpu] + [c_tensor] * 12 + [u32, u32, u32, f32]),
     "h3_gpu_gate_bf16": (
         C.c_int, [c_gpu, c_tensor, c_tensor, c_tensor, c_tensor, c_tensor, u32, u32, u32, u32]),
     "h3_gpu_gqa_causal_bf16": (

@@ -192,6 +192,32 @@ int qwcu_interleave_launch(void *full, const void *staged, uint32_t rows,
                            uint32_t slice_elements, uint32_t world, int sm_count,
                            qwcu_stream stream);
 
+/* bf16 linear layers on the tensor cores (cuda/qw_linear_sm100.cu):
+ *   c[i][m][n] = a[m][k] * w[i][n][k]^T (+ bias[i][n]) for i < n_outputs (1 or 3),
+ * fp32 accumulate, one rounding to bf16.  k and n must be multiples of 8.
+ * With norm_weight[0] / [1] set (n a multiple of 128), outputs 0 / 1 additionally
+ * get the per-head RMSNorm (bf16 [128] weight, epsilon) and the interleaved RoPE
+ * with f32 tables [table_rows][64] (table row = output row % table_rows), each
+ * stage rounded to bf16; bound_out (optional, both weights set) receives the two
+ * row-norm bounds qwcu_prologue_launch would leave. */
+typedef struct {
+    const void *a;
+    const void *w[3];
+    void *c[3];
+    const void *bias[3];
+    uint32_t n_outputs;
+    uint32_t m, k, n;
+    const void *norm_weight[2];
+    const float *rope_cos;
+    const float *rope_sin;
+    uint32_t table_rows;
+    float epsilon;
+    float *bound_out;
+    uint32_t *status;
+} qwcu_linear_args;
+
+int qwcu_linear_sm100_launch(const qwcu_linear_args *args, int sm_count, qwcu_stream stream);
+
 /* Device properties needed by the host side. */
 int qwcu_device_sm_count(int device);
 int qwcu_device_cc(int device); /* major*10 + minor */

@@ -58,7 +58,6 @@ QW_STUB_OP(h3_gpu_grouped_qkv_linear_rope_int8)
 QW_STUB_OP(h3_gpu_grouped_qkv_rope_bf16)
 QW_STUB_OP(h3_gpu_layer_norm_bf16)
 QW_STUB_OP(h3_gpu_layer_norm_f32)
-QW_STUB_OP(h3_gpu_linear_bf16)
 QW_STUB_OP(h3_gpu_linear_f32)
 QW_STUB_OP(h3_gpu_linear_int8_bf16)
 QW_STUB_OP(h3_gpu_linear_int8_head_major_bf16)
@@ -99,7 +98,6 @@ QW_STUB_OP(h3_gpu_video_qkv_rope_f32)
 QW_STUB_OP(h3_gpu_vision_qkv_rope_bf16)
 QW_STUB_OP(h3_gpu_weight_norm_f32)
 QW_STUB_OP(qw_gpu_qk_rope_half_bf16)
-QW_STUB_OP(qw_gpu_qkv_bf16)
 QW_STUB_OP(qw_gpu_rms_norm_bf16)
 QW_STUB_OP(qw_gpu_rms_norm_one_bf16)
 QW_STUB_OP(qw_gpu_swiglu_bf16)

@@ -62,6 +62,8 @@ def load():
         lib.qwo_layer_norm_mod_bf16.restype = None
         lib.qwo_gate_bf16.argtypes = [C.c_void_p] * 5 + [C.c_uint32] * 4
         lib.qwo_gate_bf16.restype = None
+        lib.qwo_linear_bf16.restype = None
+        lib.qwo_linear_bf16.argtypes = [C.c_void_p] * 4 + [C.c_uint32] * 3 + [C.c_void_p, C.c_size_t]
         lib.qwo_kat_fill.argtypes = [C.c_uint32] + [C.c_void_p] * 3 + [C.c_size_t]
         lib.qwo_kat_limits.restype = None
         lib.qwo_kat_limits.argtypes = [C.c_void_p]
@@ -199,3 +201,15 @@ def prefix_limits(segments):
     out = np.zeros(sum(r for r, _ in segments), np.uint32)
     lib.qwo_prefix_limits(arr, len(segments), _p(out))
     return out
+
+
+def linear(x, weight, bias, rows, input_dim, output_dim, row_index=None):
+    """bf16 linear layer (bits in, bits out); row_index = rows to compute (others 0)."""
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    weight = np.ascontiguousarray(weight, dtype=np.uint16)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.uint16)
+    idx = None if row_index is None else np.ascontiguousarray(row_index, dtype=np.uint32)
+    out = np.zeros(rows * output_dim, np.uint16)
+    load().qwo_linear_bf16(_p(out), _p(x), _p(weight), _p(b), rows, input_dim, output_dim, _p(idx),
+                           0 if idx is None else idx.size)
+    return out.reshape(rows, output_dim)
