@@ -175,7 +175,11 @@ int h3_gpu_gqa_causal_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tens
  * exceed 4,194,304 (larger calls fail with an error; use the regular op).  The
  * array is shared by all calls on a GPU: calls that overlap on one GPU race and
  * must be serialised by the caller.  The first call on a device resolves the
- * array's address; make it before starting any stream capture.  Requires
+ * array's address; make it before starting any stream capture.  That first call
+ * is also the one moment this entry point can need memory: with lazy module
+ * loading it is when the driver loads this kernel's module and sets the 8 MiB
+ * array aside, so make it (or run with CUDA_MODULE_LOADING=EAGER) before the
+ * host's arena claims the GPU; every later call allocates nothing.  Requires
  * head_dim == 128 and a positive finite scale. */
 int h3_gpu_gqa_causal_noalloc_bf16(h3_gpu *gpu, h3_gpu_tensor *output,
                                    const h3_gpu_tensor *query, const h3_gpu_tensor *key,

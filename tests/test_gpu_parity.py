@@ -275,6 +275,20 @@ def test_large_configs_row_sample(gpu, tail_form, index, count):
             assert not out[b, tl:w.text_pad].any()
 
 
+@pytest.mark.parametrize("layer", [7, 19, 31])
+@pytest.mark.parametrize("index,count", [(3, 48), (4, 40), (5, 24)])
+def test_large_configs_other_layer_seeds(gpu, index, count, layer):
+    """The 32 layers of a workload are 32 different seeded inputs: beside layer 0
+    (above, in every kernel form) three more seeds of every large configuration, a
+    few dozen rows each plus the run / padding boundaries."""
+    w = workloads.workload(index)
+    inputs, out = run_workload_layer(gpu, w, layer=layer)
+    rows = sample_rows(w, count, seed=100 + layer)
+    ref = oracle_layer(w, inputs, rows)
+    flat = out.reshape(w.batch * w.rows, w.heads, 128)
+    gates(flat[rows], ref.reshape(flat.shape)[rows], f"cfg{index} layer {layer}, {rows.size} rows")
+
+
 def test_cfg3_sm100_agrees_with_scalar_kernel_everywhere(gpu):
     """Whole-output cross-check on the GPU at a size the CPU oracle only samples."""
     w = workloads.workload(3)
@@ -342,13 +356,20 @@ def test_score_bound_is_an_upper_bound_and_loose_bounds_fall_back(gpu):
 # --------------------------------------------------------------------------
 # integer mask indexing, bit-exact on the device
 # --------------------------------------------------------------------------
-def test_split_blocks_agree_with_whole_blocks(gpu):
-    """cfg3 with 3 heads (what one of eight GPUs runs): 102 blocks on 148 SMs, so
-    the default splits 46 of them in two.  The merged halves agree with the same
-    blocks run whole within the parity gates (P is rounded to bf16 relative to a
-    reference exponent that depends on where the keys were cut, so not bit for
-    bit), and two runs of the split form are bit-identical."""
-    w = dataclasses.replace(workloads.workload(3), heads=3, prologue=False)
+@pytest.mark.parametrize("prologue", [False, True])
+def test_split_blocks_agree_with_whole_blocks(gpu, prologue):
+    """cfg3 with 6 heads (what one of four GPUs runs): 204 blocks on 148 SMs, so the
+    default runs the 56 blocks of the second wave split in two (half the rows each,
+    the key tiles divided between the sub-tiles, merged inside the CTA).  The merged
+    halves agree with the same blocks run whole within the parity gates (with the
+    running maximum, P is rounded to bf16 relative to a reference exponent that
+    depends on where the keys were cut, so not bit for bit), and two runs of the
+    split form are bit-identical.  With the prologue the fixed-exponent softmax runs."""
+    gpu.lib.qwcu_attn_sm100_tail_units.restype = C.c_uint32
+    gpu.lib.qwcu_attn_sm100_tail_units.argtypes = [C.c_uint32, C.c_uint32]
+    w = dataclasses.replace(workloads.workload(3), heads=6, prologue=prologue)
+    units = w.batch * w.heads * ((w.rows + 255) // 256)
+    assert units == 204 and gpu.lib.qwcu_attn_sm100_tail_units(units, 148) == 56
     _, first = run_workload_layer(gpu, w)
     _, second = run_workload_layer(gpu, w)
     assert np.array_equal(first, second)
@@ -357,6 +378,7 @@ def test_split_blocks_agree_with_whole_blocks(gpu):
         _, whole = run_workload_layer(gpu, w)
     finally:
         gpu.lib.qw_gpu_set_attention_kernel(gpu.handle, b"sm100")
+    assert not np.array_equal(first, whole) or prologue   # really two different schedules
     gates(first, bf16_to_f32(whole), "split vs whole blocks")
 
 
