@@ -6,18 +6,23 @@
 A step is one 32-layer attention pass (per layer: fused QK-norm + RoPE, then
 block-causal attention) over seeded synthetic inputs of the 1024^2 CFG workload
 (batch 2, text 200 / 32 padded to 256, 4096 image tokens, 24 heads x 128).
-With N > 1 (launched by torch.distributed.run, one rank per GPU) the heads are
-sharded N ways and every layer's [rows, heads*128] output is all-gathered with
-NCCL; the total work is fixed (strong scaling).
+With N > 1 (launched by torch.distributed.run, one rank per GPU) the ranks form
+batch groups x head groups: the two guidance branches go to different ranks
+first (they never exchange anything), then the heads are sharded and every
+layer's [rows, heads*128] output is gathered inside a batch group by the
+library's own push kernel over NVLink; the total work is fixed (strong scaling).
 
 Prints ONE JSON line: whole-job mask-aware TFLOP/s (`value`, inputs resident in
-HBM), the same metric end to end from pinned HOST buffers through the C ABI
-(`e2e`), the dominant kernel's roofline, the CPU oracle timed beside it
-(`cpu_baseline`) and the clocks seen during the timed region.
+HBM), the parity of what the timed step wrote against the CPU oracle on every
+rank (`parity`; the run exits non-zero on a miss), the same metric end to end
+from pinned HOST buffers through the C ABI (`e2e`), the dominant kernel's
+roofline, the same for the largest configuration (`sweep_cfg5`), the CPU oracle
+timed beside it (`cpu_baseline`) and the clocks seen during the timed region.
 
 --impl reference times the CPU implementation of the path (the oracle port of
 the reference's tests/test_prefix_kernel.c loop plus its scalar norm / RoPE
-arithmetic, OpenMP over rows) on the host cores for the same metric.
+arithmetic, OpenMP over rows) on the host cores for the same metric; it loads
+nothing of the product library.
 """
 import argparse
 import json
@@ -705,7 +710,8 @@ def run_product(args):
     ctx = Context(args)
     gpu, lib, world, rank = ctx.gpu, ctx.gpu.lib, ctx.world, ctx.rank
     peaks = measured_peaks()
-    job = Job(ctx, args.workload, layers=args.layers, gather=args.gather, cfg_split=args.cfg_split)
+    job = Job(ctx, args.workload, layers=args.layers, distinct_layers=args.distinct_layers,
+              gather=args.gather, cfg_split=args.cfg_split)
     w = job.w
     sampler = ClockSampler(ctx.local)
     if rank == 0:
@@ -871,6 +877,9 @@ def main():
     ap.add_argument("--workload", type=int, default=3, choices=[2, 3, 4, 5])
     ap.add_argument("--layers", type=int, default=0,
                     help="override the layer count (small captures under a profiler)")
+    ap.add_argument("--distinct-layers", type=int, default=0,
+                    help="generate only this many distinct seeded input sets and cycle them over "
+                         "the layers (quick experiments; default: one per layer)")
     ap.add_argument("--gather", default="push", choices=["push", "nccl"],
                     help="head groups > 1: the library's push kernel over peer memory, or NCCL "
                          "all-gather + interleave (comparison; needs --no-cfg-split)")

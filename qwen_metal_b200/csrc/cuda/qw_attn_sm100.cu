@@ -1595,15 +1595,16 @@ bool whole_units_forced() {
     return forced != 0;
 }
 
-// QW_CUDA_SOFTMAX_ORG=row: run the fixed-exponent softmax with one thread per row
-// (one warpgroup per sub-tile) instead of the paired organisation (comparison runs).
-bool row_org_forced() {
-    static int forced = -1;
-    if (forced < 0) {
+// QW_CUDA_SOFTMAX_ORG=row / pair: force the organisation of the fixed-exponent
+// softmax (one thread per row, or both warpgroups on one sub-tile's keys at a time)
+// instead of choosing by the length of the launch (comparison runs).  -1 = not set.
+int softmax_org_forced() {
+    static int forced = -2;
+    if (forced == -2) {
         const char *env = getenv("QW_CUDA_SOFTMAX_ORG");
-        forced = env && !strcmp(env, "row") ? 1 : 0;
+        forced = !env ? -1 : !strcmp(env, "row") ? 0 : !strcmp(env, "pair") ? 1 : -1;
     }
-    return forced != 0;
+    return forced;
 }
 
 // The kernel variants: how many of every 4 score pairs take the polynomial exp2
@@ -1681,7 +1682,7 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
     p.text_pad = a->text_pad;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.score_bound = a->score_bound;
-    p.pair_org = (a->row_softmax || row_org_forced()) ? 0 : 1;
+    p.pair_org = -1;  // decided below, once the unit count is known
     p.head_major_out = a->head_major_out;
     if (a->n_out_peers > 0) {
         if (a->n_out_peers > 8 || a->head_major_out) return (int)cudaErrorInvalidValue;
@@ -1722,6 +1723,16 @@ extern "C" int qwcu_attn_sm100_launch(const qwcu_attn_args *a, qwcu_stream strea
                        ? 0u
                        : qwcu_attn_sm100_tail_units(p.total_units,
                                                     (uint32_t)sm_count_of_current_device());
+    // Fixed-exponent softmax: paired organisation where the launch is short (at most
+    // two waves of CTAs: the per-tile latency chain is what bounds it), one thread per
+    // row where it is long (many waves run at the board's power limit, where the
+    // organisation with fewer instructions per score is the faster one).
+    {
+        const int forced = softmax_org_forced();
+        const bool long_launch =
+            p.total_units > 2u * (uint32_t)sm_count_of_current_device();
+        p.pair_org = a->row_softmax ? 0 : forced >= 0 ? forced : long_launch ? 0 : 1;
+    }
     const unsigned grid = p.total_units + p.tail_units;
     kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, maps_out, p);
     rc = (int)cudaGetLastError();
