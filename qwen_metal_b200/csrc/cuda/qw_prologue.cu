@@ -178,15 +178,16 @@ __global__ void qw_scale_bf16_kernel(__nv_bfloat16 *out, const __nv_bfloat16 *in
     }
 }
 
+// SM count of the current device (a process may drive several devices).
 int sm_count_cached() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
+    static int sms[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) {
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (sms[dev] <= 0) sms[dev] = 148;
     }
-    return sms;
+    return sms[dev];
 }
 
 }  // namespace
