@@ -194,7 +194,7 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
     group->world = world;
     group->sm_count = qwcu_device_sm_count(gpu->device);
     /* CTAs of the push kernel and the budget of its flag waits (tuning / tests). */
-    group->push_blocks = env_u32("QW_CUDA_GROUP_PUSH_BLOCKS", 128);
+    group->push_blocks = env_u32("QW_CUDA_GROUP_PUSH_BLOCKS", 0); /* 0 = by the launch shape */
     group->wait_ms = env_u32("QW_CUDA_GROUP_WAIT_MS", 2000);
     group_layout(group, 1);
     nccl_unique_id id;
@@ -482,6 +482,22 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
     push.status = gpu->status_dev;
     push.wait_ms = group->wait_ms;
     push.max_blocks = group->push_blocks;
+    if (!push.max_blocks) {
+        /* The push runs beside the NEXT layer's attention.  Where that is a single,
+         * partly filled wave of CTAs (few heads per GPU) the idle SMs carry two push
+         * CTAs each; where the attention fills the device, a small grid that slips in
+         * as CTAs retire disturbs it least (measured: 32 CTAs expose 14 us per layer
+         * at 2 GPUs, 128 expose 40). */
+        uint64_t units = (uint64_t)batch * heads_local * ((rows + 255) / 256);
+        uint32_t sms = group->sm_count > 0 ? (uint32_t)group->sm_count : 148u;
+        uint32_t blocks = 32;
+        if (units < sms) {
+            blocks = (uint32_t)(sms - units) * 2u;
+            if (blocks < 32) blocks = 32;
+            if (blocks > 128) blocks = 128;
+        }
+        push.max_blocks = blocks;
+    }
     int rc = qwcu_push_launch(&push, group->comm_stream);
     qw_count_launch(gpu, rc, "head push");
     if (rc) return 0;
