@@ -354,8 +354,7 @@ static uint64_t sdpa_row(float *out, const uint16_t *q, const uint16_t *k,
                          uint32_t q_rows, uint32_t kv_rows, uint32_t heads,
                          uint32_t kv_heads, uint32_t D, float scale,
                          const uint32_t *text_len, uint32_t text_pad, float *scores,
-                         float *kf) {
-    (void)kf;
+                         const float *kf, const float *vf) {
     int padded_query = text_len && r >= text_len[b] && r < text_pad;
     uint64_t visible = 0;
     for (uint32_t h = 0; h < heads; h++) {
@@ -373,9 +372,15 @@ static uint64_t sdpa_row(float *out, const uint16_t *q, const uint16_t *k,
                 scores[s] = 0.0f;
                 continue;
             }
-            const uint16_t *kv = k + (((size_t)b * kv_rows + s) * kv_heads + kvh) * D;
+            const size_t at = (((size_t)b * kv_rows + s) * kv_heads + kvh) * D;
             float dot = 0.0f;
-            for (uint32_t d = 0; d < D; d++) dot += qf[d] * qwo_bf16_to_f32(kv[d]);
+            if (kf) { /* keys already widened to fp32, as the reference's arrays are */
+                const float *kr = kf + at;
+                for (uint32_t d = 0; d < D; d++) dot += qf[d] * kr[d];
+            } else {
+                const uint16_t *kv = k + at;
+                for (uint32_t d = 0; d < D; d++) dot += qf[d] * qwo_bf16_to_f32(kv[d]);
+            }
             scores[s] = dot * scale;
             if (scores[s] > m) m = scores[s];
             count++;
@@ -390,9 +395,15 @@ static uint64_t sdpa_row(float *out, const uint16_t *q, const uint16_t *k,
         }
         for (uint32_t s = 0; s < limit; s++) {
             if (!key_visible(s, limit, text_len, b, text_pad)) continue;
-            const uint16_t *vv = v + (((size_t)b * kv_rows + s) * kv_heads + kvh) * D;
+            const size_t at = (((size_t)b * kv_rows + s) * kv_heads + kvh) * D;
             float p = scores[s] / denom;
-            for (uint32_t d = 0; d < D; d++) o[d] += p * qwo_bf16_to_f32(vv[d]);
+            if (vf) {
+                const float *vr = vf + at;
+                for (uint32_t d = 0; d < D; d++) o[d] += p * vr[d];
+            } else {
+                const uint16_t *vv = v + at;
+                for (uint32_t d = 0; d < D; d++) o[d] += p * qwo_bf16_to_f32(vv[d]);
+            }
         }
     }
     return visible;
@@ -408,6 +419,27 @@ uint64_t qwo_sdpa_prefix(float *out, const uint16_t *q, const uint16_t *k,
     if (head_dim > 256 || !heads || !kv_heads) return 0;
     size_t total_rows = row_index ? n_rows : (size_t)batch * q_rows;
     uint64_t visible_total = 0;
+    /* The reference's loop runs on fp32 copies of the bf16 inputs
+     * (tests/test_prefix_kernel.c:51-63): widen K and V once instead of inside the
+     * dot products (same values, same order of operations; falls back to widening
+     * in place when the copies do not fit). */
+    const size_t kv_count = (size_t)batch * kv_rows * kv_heads * head_dim;
+    float *kf = NULL, *vf = NULL;
+    if (total_rows >= 64) {
+        kf = (float *)malloc(kv_count * sizeof(float));
+        vf = (float *)malloc(kv_count * sizeof(float));
+        if (kf && vf) {
+#pragma omp parallel for schedule(static)
+            for (int64_t i = 0; i < (int64_t)kv_count; i++) {
+                kf[i] = qwo_bf16_to_f32(k[i]);
+                vf[i] = qwo_bf16_to_f32(v[i]);
+            }
+        } else {
+            free(kf);
+            free(vf);
+            kf = vf = NULL;
+        }
+    }
 #pragma omp parallel reduction(+ : visible_total)
     {
         float *scores = (float *)malloc(sizeof(float) * (kv_rows ? kv_rows : 1));
@@ -421,9 +453,11 @@ uint64_t qwo_sdpa_prefix(float *out, const uint16_t *q, const uint16_t *k,
             if (scores)
                 visible_total += sdpa_row(out, q, k, v, b, r, limit, q_rows, kv_rows,
                                           heads, kv_heads, head_dim, scale, text_len,
-                                          text_pad, scores, NULL);
+                                          text_pad, scores, kf, vf);
         }
         free(scores);
     }
+    free(kf);
+    free(vf);
     return visible_total;
 }
