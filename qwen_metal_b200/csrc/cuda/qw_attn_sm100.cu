@@ -23,9 +23,19 @@
 //
 // Epilogue: O / l is rounded to bf16 into the (by then dead) Q tile in shared
 // memory and leaves as TMA stores of the whole 128x128 tile.  When the heads
-// are sharded over several GPUs the same tile is stored into every rank's full
-// output through peer-mapped pointers, so the per-layer gather costs no extra
-// pass: the transfer is issued tile by tile while other tiles still compute.
+// are sharded over several GPUs the tile goes to this rank's head columns of a
+// full-width output (the kernel can address several such destinations, peer-
+// mapped ones included); the multi-GPU group writes the rank's own buffer here
+// and carries the columns to the peers with a push kernel under the next layer,
+// because with a single wave of CTAs all peer stores would leave at the kernel's
+// end as one exposed burst.  At its start the kernel then opens the output slot's
+// next epoch for the peers' pushes.
+//
+// Softmax.  Callers that promise bounded row norms (the DiT layer's QK-norm) get
+// P = exp2(score*c - bound) against one fixed exponent: no row maximum, no
+// rescaling, scores streamed out of TMEM in 32-column chunks; short launches pair
+// both warpgroups on one sub-tile's keys at a time.  Other callers get the
+// running maximum with lazy rescaling.
 //
 // Wave tail.  The grid is one CTA per (batch, head, 256-row block), heaviest
 // blocks first, and rarely a multiple of the SM count.  The units that would
@@ -136,8 +146,8 @@ struct KernelParams {
     const float *score_bound;
     int pair_org;  // fixed-exponent softmax: both warpgroups share each sub-tile's keys
     int head_major_out;
-    // Sharded runs: the same rows are stored into every rank's full output
-    // (peer-mapped pointers, plain stores over NVLink).  out_heads_total is the
+    // Sharded runs: the rows are stored at this rank's head columns of n_out
+    // full-width outputs (peer-mapped pointers allowed).  out_heads_total is the
     // head count of the destination rows and out_head_offset this rank's first head.
     __nv_bfloat16 *out_peers[8];
     uint32_t n_out, out_heads_total, out_head_offset;
