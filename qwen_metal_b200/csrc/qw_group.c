@@ -219,7 +219,16 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
     group->sync_peer[rank] = sync_local;
     cudaMemset(group->exchange, 0, QW_GROUP_MAX_WORLD * QW_IPC_HANDLE_BYTES + 16);
     cudaMemset(sync_local, 0, QW_SYNC_WORDS * sizeof(uint32_t));
-    int ok = cudaStreamCreateWithFlags(&group->comm_stream, cudaStreamNonBlocking) == cudaSuccess &&
+    /* The communication stream gets the highest priority: when SMs free up between
+     * the next layer's kernels, the few CTAs of the push are placed first and finish
+     * early instead of queueing behind a full wave of attention CTAs. */
+    int least = 0, greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) {
+        cudaGetLastError();
+        greatest = 0;
+    }
+    int ok = cudaStreamCreateWithPriority(&group->comm_stream, cudaStreamNonBlocking, greatest) ==
+                 cudaSuccess &&
              cudaEventCreateWithFlags(&group->kernel_done, cudaEventDisableTiming) == cudaSuccess;
     for (int b = 0; ok && b < QW_GROUP_MAX_BOUND; b++)
         ok = cudaEventCreateWithFlags(&group->slot_done[b], cudaEventDisableTiming) == cudaSuccess;
@@ -483,18 +492,26 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
     push.wait_ms = group->wait_ms;
     push.max_blocks = group->push_blocks;
     if (!push.max_blocks) {
-        /* The push runs beside the NEXT layer's attention.  Where that is a single,
-         * partly filled wave of CTAs (few heads per GPU) the idle SMs carry two push
-         * CTAs each; where the attention fills the device, a small grid that slips in
-         * as CTAs retire disturbs it least (measured: 32 CTAs expose 14 us per layer
-         * at 2 GPUs, 128 expose 40). */
+        /* The push runs beside the NEXT layer's attention and should be done well
+         * before it.  A CTA of the push moves about 5.6 MB/ms over NVLink (measured:
+         * 32 CTAs, 180 GB/s); the attention takes roughly waves x key tiles x 1.7 us.
+         * So: enough CTAs to finish in ~70 % of that time, at least 32 (a small grid
+         * that slips in as attention CTAs retire disturbs a full device least: 32
+         * CTAs expose 14 us per layer at 2 GPUs, 128 expose 40), and where the
+         * attention is a single, partly filled wave (few heads per GPU) two per SM it
+         * leaves idle. */
         uint64_t units = (uint64_t)batch * heads_local * ((rows + 255) / 256);
         uint32_t sms = group->sm_count > 0 ? (uint32_t)group->sm_count : 148u;
-        uint32_t blocks = 32;
+        double waves = (double)units / sms;
+        if (waves < 1.0) waves = 1.0;
+        double attention_us = waves * ((double)rows / 128.0) * 1.7;
+        double bytes_out = (double)push.rows * push.slice_bytes * group->n_peers;
+        double want = 1.4 * bytes_out / (attention_us * 5600.0);
+        uint32_t blocks = want > 128.0 ? 128u : want < 32.0 ? 32u : (uint32_t)want;
         if (units < sms) {
-            blocks = (uint32_t)(sms - units) * 2u;
-            if (blocks < 32) blocks = 32;
-            if (blocks > 128) blocks = 128;
+            uint32_t idle = (uint32_t)(sms - units) * 2u;
+            if (idle > 128) idle = 128;
+            if (idle > blocks) blocks = idle;
         }
         push.max_blocks = blocks;
     }
