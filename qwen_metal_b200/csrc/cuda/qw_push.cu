@@ -160,6 +160,37 @@ __global__ void __launch_bounds__(kPushThreads) qw_push_kernel(const PushParams 
     }
 }
 
+// Copy-engine form: the same hand-shake around plain strided device-to-device
+// copies (one per peer), which need no SM at all.  One warp waits for the peers'
+// `freed` flags before the copies; one warp publishes `ready` after them and
+// waits for the peers' own.  (A wait that ran out is reported; the copies after
+// it are part of the stream and still run.)
+__global__ void __launch_bounds__(32) qw_push_open_kernel(const PushParams p) {
+    if (threadIdx.x >= p.n_peers) return;
+    const uint32_t epoch = *reinterpret_cast<const volatile uint32_t *>(p.slot_use);
+    const uint32_t d = threadIdx.x;
+    if (!wait_epoch(p.freed_local + p.peer_rank[d], epoch, p.budget_ns) &&
+        atomicCAS(p.status, 0u, (uint32_t)QWCU_STATUS_WAIT_TIMEOUT) == 0u) {
+        p.status[1] = 0x50000u | p.peer_rank[d];
+        p.status[2] = epoch;
+        p.status[3] = 0;
+    }
+}
+
+__global__ void __launch_bounds__(32) qw_push_close_kernel(const PushParams p) {
+    if (threadIdx.x >= p.n_peers) return;
+    const uint32_t epoch = *reinterpret_cast<const volatile uint32_t *>(p.slot_use);
+    const uint32_t d = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(p.ready_peer[d], epoch);
+    if (!wait_epoch(p.ready_local + p.peer_rank[d], epoch, p.budget_ns) &&
+        atomicCAS(p.status, 0u, (uint32_t)QWCU_STATUS_WAIT_TIMEOUT) == 0u) {
+        p.status[1] = 0x60000u | p.peer_rank[d];
+        p.status[2] = epoch;
+        p.status[3] = 0;
+    }
+}
+
 }  // namespace
 
 extern "C" int qwcu_push_launch(const qwcu_push_args *a, qwcu_stream stream_) {
@@ -192,6 +223,20 @@ extern "C" int qwcu_push_launch(const qwcu_push_args *a, qwcu_stream stream_) {
     p.arrivals = a->arrivals;
     p.status = a->status;
     p.budget_ns = (unsigned long long)(a->wait_ms ? a->wait_ms : 2000u) * 1000000ull;
+    if (a->copy_engine) {
+        qw_push_open_kernel<<<1, 32, 0, stream>>>(p);
+        int rc = (int)cudaGetLastError();
+        if (rc) return rc;
+        const char *src = static_cast<const char *>(a->src) + a->col_byte0;
+        for (uint32_t d = 0; d < a->n_peers; ++d) {
+            char *dst = static_cast<char *>(a->dst[d]) + a->col_byte0;
+            rc = (int)cudaMemcpy2DAsync(dst, a->row_bytes, src, a->row_bytes, a->slice_bytes, a->rows,
+                                        cudaMemcpyDeviceToDevice, stream);
+            if (rc) return rc;
+        }
+        qw_push_close_kernel<<<1, 32, 0, stream>>>(p);
+        return (int)cudaGetLastError();
+    }
     unsigned long long items = (unsigned long long)p.rows * p.slice_vecs;
     unsigned long long want = (items + (unsigned long long)kPushThreads * kInFlight - 1) /
                               ((unsigned long long)kPushThreads * kInFlight);

@@ -182,6 +182,9 @@ typedef struct {
     uint32_t *status;
     uint32_t wait_ms;    /* budget of every flag wait (0 = 2000 ms) */
     uint32_t max_blocks; /* CTAs of 256 threads (0 = 32) */
+    /* Move the bytes with strided device-to-device copies (copy engines, no SM)
+     * between two one-warp hand-shake kernels, instead of the copy kernel. */
+    int copy_engine;
 } qwcu_push_args;
 
 int qwcu_push_launch(const qwcu_push_args *args, qwcu_stream stream);

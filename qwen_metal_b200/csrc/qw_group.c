@@ -107,6 +107,7 @@ struct qw_gpu_group {
     int slot_pending[QW_GROUP_MAX_BOUND];
     uint32_t slot_capture[QW_GROUP_MAX_BOUND]; /* capture the slot's event belongs to (0 = none) */
     uint32_t push_blocks, wait_ms;
+    int push_copy_engine; /* QW_CUDA_GROUP_PUSH=ce: copy engines move the bytes */
 };
 
 static void group_layout(qw_gpu_group *group, int batch_groups) {
@@ -196,6 +197,10 @@ qw_gpu_group *qw_gpu_group_join(h3_gpu *gpu, const void *id_bytes, int rank, int
     /* CTAs of the push kernel and the budget of its flag waits (tuning / tests). */
     group->push_blocks = env_u32("QW_CUDA_GROUP_PUSH_BLOCKS", 0); /* 0 = by the launch shape */
     group->wait_ms = env_u32("QW_CUDA_GROUP_WAIT_MS", 2000);
+    {
+        const char *mode = getenv("QW_CUDA_GROUP_PUSH");
+        group->push_copy_engine = mode && !strcmp(mode, "ce");
+    }
     group_layout(group, 1);
     nccl_unique_id id;
     memcpy(&id, id_bytes, sizeof(id));
@@ -515,8 +520,10 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
         }
         push.max_blocks = blocks;
     }
+    push.copy_engine = group->push_copy_engine;
     int rc = qwcu_push_launch(&push, group->comm_stream);
     qw_count_launch(gpu, rc, "head push");
+    if (!rc && push.copy_engine) qw_count_launch(gpu, 0, "head push"); /* two small kernels */
     if (rc) return 0;
     if (!qw_cuda_ok(gpu, cudaEventRecord(group->slot_done[slot_index], group->comm_stream),
                     "group attention"))
