@@ -502,9 +502,10 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
          * 32 CTAs, 180 GB/s); the attention takes roughly waves x key tiles x 1.7 us.
          * So: enough CTAs to finish in ~70 % of that time, at least 32 (a small grid
          * that slips in as attention CTAs retire disturbs a full device least: 32
-         * CTAs expose 14 us per layer at 2 GPUs, 128 expose 40), and where the
-         * attention is a single, partly filled wave (few heads per GPU) two per SM it
-         * leaves idle. */
+         * CTAs expose 14 us per layer at 2 GPUs, 128 expose 40).  Where the attention
+         * is a single, partly filled wave (few heads per GPU) the layer is short and
+         * the small grid wins as well: at 8 GPUs 32 CTAs exposed 19 us per layer, two
+         * CTAs per idle SM (92) exposed 34 us. */
         uint64_t units = (uint64_t)batch * heads_local * ((rows + 255) / 256);
         uint32_t sms = group->sm_count > 0 ? (uint32_t)group->sm_count : 148u;
         double waves = (double)units / sms;
@@ -513,11 +514,7 @@ int qw_gpu_group_attn_block_causal_bf16(qw_gpu_group *group, h3_gpu_tensor *full
         double bytes_out = (double)push.rows * push.slice_bytes * group->n_peers;
         double want = 1.4 * bytes_out / (attention_us * 5600.0);
         uint32_t blocks = want > 128.0 ? 128u : want < 32.0 ? 32u : (uint32_t)want;
-        if (units < sms) {
-            uint32_t idle = (uint32_t)(sms - units) * 2u;
-            if (idle > 128) idle = 128;
-            if (idle > blocks) blocks = idle;
-        }
+        if (units < sms) blocks = 32u;
         push.max_blocks = blocks;
     }
     push.copy_engine = group->push_copy_engine;
