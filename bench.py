@@ -628,7 +628,9 @@ def gather_record(ctx, job, steps, attention_ms):
 
     layer_s = ctx.timed(sharded_attention, steps) / (steps * w.layers)
     slice_bytes = job.nb * w.rows * job.heads_local * 128 * 2
-    return {"mode": "push kernel over peer-mapped memory (NVLink), flag hand-shake, no NCCL call",
+    form = ("copy engines (one strided copy per peer) between two flag kernels"
+            if os.environ.get("QW_CUDA_GROUP_PUSH") == "ce" else "push kernel")
+    return {"mode": form + " over peer-mapped memory (NVLink), flag hand-shake, no NCCL call",
             "peers": job.head_groups - 1,
             "nvlink_bytes_out_per_launch": slice_bytes * (job.head_groups - 1),
             "attention_plus_push_ms_per_layer": layer_s * 1e3,
